@@ -1,0 +1,221 @@
+/*
+ * b200moe.h -- C ABI of the B200 (sm_100a) expert-parallel quantized MoE kernels.
+ *
+ * One shared library, plain pointers and sizes, no framework types.  Every
+ * function launches asynchronously on the CUDA stream it is given (a
+ * cudaStream_t passed as void*; NULL = the legacy default stream), never
+ * allocates or frees device memory, never synchronises, and returns a status
+ * code (0 = ok).  All pointers are device pointers unless stated otherwise;
+ * all tensors are dense row-major unless a stride is an argument.
+ *
+ * Each entry point names the reference interface it stands in for (paths are
+ * relative to the reference project root).
+ */
+#ifndef B200MOE_H_
+#define B200MOE_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define B200MOE_API __attribute__((visibility("default")))
+#else
+#define B200MOE_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes (the reference returns 0 / -1 from simple_marlin_cuda,
+ *      fast_dequant/simple_marlin/marlin_w4a16_gemm.cu:300-302,325, and raises
+ *      from bare asserts in its Python wrappers) ---- */
+enum {
+  B200MOE_OK = 0,
+  B200MOE_BAD_SHAPE = 1,         /* a size the kernel does not support            */
+  B200MOE_BAD_ALIGN = 2,         /* pointer or stride not aligned as required     */
+  B200MOE_BAD_DTYPE = 3,
+  B200MOE_BAD_ARG = 4,           /* null pointer, inconsistent arguments          */
+  B200MOE_WORKSPACE_TOO_SMALL = 5,
+  B200MOE_LAUNCH_FAILED = 6,     /* CUDA reported an error at launch              */
+  B200MOE_DEVICE_TIMEOUT = 7,    /* a bounded device-side wait expired            */
+  B200MOE_UNSUPPORTED_DEVICE = 8 /* not an sm_100 device / driver too old         */
+};
+
+/* ---- element types ---- */
+enum {
+  B200MOE_F32 = 0,
+  B200MOE_F16 = 1,
+  B200MOE_BF16 = 2,
+  B200MOE_FP8_E4M3 = 3,
+  B200MOE_I8 = 4
+};
+
+B200MOE_API const char* b200moe_status_string(int status);
+/* Message of the last non-zero status returned on the calling host thread. */
+B200MOE_API const char* b200moe_last_error(void);
+B200MOE_API int b200moe_abi_version(void);
+
+/* ======================= quantization/fp8_kernel.py ======================= */
+
+/* act_quant (quantization/fp8_kernel.py:33-52; kernel :9-30).
+ * x [rows, cols] (f32/f16/bf16), cols % 128 == 0.  Per 128 contiguous values
+ * s = amax/448 (f32) and y = e4m3(x / s), round-to-nearest-even.  amax == 0
+ * gives s == 0 and y == NaN, as in the reference.
+ * y [rows, cols] e4m3 with row stride y_row_stride_bytes, s [rows, cols/128]
+ * f32 with row stride s_row_stride (in floats). */
+B200MOE_API int b200moe_act_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                          void* y, int64_t y_row_stride_bytes,
+                          float* s, int64_t s_row_stride, void* stream);
+
+/* weight_dequant (quantization/fp8_kernel.py:84-105): y = x * s[i/128, j/128]. */
+B200MOE_API int b200moe_weight_dequant_fp8(const void* x, const float* s, void* y, int y_dtype,
+                               int64_t M, int64_t N, void* stream);
+
+/* 128x128-block e4m3 weight quantizer, s = amax/448.  The reference ships the
+ * int8 form only (quantization/int8_kernel.py:59-113); this is its fp8 twin
+ * with the same block grid and scale shape [ceil(M/128), ceil(N/128)]. */
+B200MOE_API int b200moe_weight_quant_fp8(const void* w, int w_dtype, void* y, float* s,
+                             int64_t M, int64_t N, void* stream);
+
+/* fp8_gemm (quantization/fp8_kernel.py:170-190; kernel :108-167).
+ * c[M,N] = a[M,K] . b[N,K]^T with acc += dot_kb * a_s[m,kb] * b_s[n/128,kb]
+ * per 128-wide K block.  a, b e4m3; a_s [M,K/128], b_s [N/128,K/128] f32;
+ * c f32/f16/bf16.  K % 128 == 0, N % 128 == 0; a, b 16-byte aligned. */
+B200MOE_API int b200moe_gemm_fp8_block(const void* a, const float* a_s, const void* b, const float* b_s,
+                           void* c, int c_dtype, int64_t M, int64_t N, int64_t K,
+                           void* stream);
+
+/* ======================= quantization/int8_kernel.py ====================== */
+
+/* act_quant: s = amax/127 stored as f16, y = round(x/s) as int8.
+ * rounding 0 = half away from zero (quantization/int8_kernel.py:23-31),
+ *          1 = floor(v + 0.5)      (quantization/w4a8_kernel.py:159-168). */
+B200MOE_API int b200moe_act_quant_int8(const void* x, int x_dtype, int64_t rows, int64_t cols,
+                           void* y, void* s_f16, int rounding, void* stream);
+
+/* ========================= moe/all2all_moe.py ============================= */
+
+/* MoEGate.forward (moe/all2all_moe.py:60-118).
+ * logits = x[T,H] (f32/f16/bf16) . w[E,H]^T (f32) in f32; scoring 0 = sigmoid,
+ * 1 = softmax over experts; selection scores = scores + bias (bias may be
+ * NULL); group-limited top-k: group score = sum of its top 2, keep topk_group
+ * of n_group groups, other experts' selection scores become 0.0, then top_k.
+ * Ties go to the lower expert id.  topk_weight gathers the unbiased scores,
+ * divides by (sum + 1e-20) when norm_topk_prob and top_k > 1, and multiplies
+ * by routed_scaling_factor.  topk_idx int64 [T,top_k] in descending selection
+ * score order; topk_weight f32 [T,top_k].  E <= 256, E % n_group == 0,
+ * top_k <= 32, H % 8 == 0. */
+B200MOE_API int b200moe_router_topk(const void* x, int x_dtype, const float* w, const float* bias,
+                        int64_t T, int64_t H, int E, int top_k, int n_group, int topk_group,
+                        int scoring, int norm_topk_prob, float routed_scaling_factor,
+                        int64_t* topk_idx, float* topk_weight, void* stream);
+
+/* ======================= moe/group_gemm_kernel.py ========================= */
+
+/* run_moe_ep_preproess (moe/group_gemm_kernel.py:48-78): stable counting sort
+ * of the num_slots = T*k expert ids.
+ *   reorder_topk_ids int64 [num_slots]  ids in sorted order        (:52)
+ *   src2dst          int32 [num_slots]  flat slot -> sorted row    (:37-45)
+ *   seg_indptr       int64 [E+1]        exclusive prefix of counts (:19-34)
+ * workspace: b200moe_route_metadata_workspace_bytes() bytes of scratch,
+ * 16-byte aligned.  Bit-exact and deterministic (no order-dependent atomics).
+ * num_experts <= 1024. */
+B200MOE_API size_t b200moe_route_metadata_workspace_bytes(int64_t num_slots, int num_experts);
+B200MOE_API int b200moe_route_metadata(const int64_t* topk_ids, int64_t num_slots, int num_experts,
+                           int64_t* reorder_topk_ids, int32_t* src2dst, int64_t* seg_indptr,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* pre_reorder_triton_kernel (moe/group_gemm_kernel.py:81-117): for every slot
+ * whose expert is in [start_expert_id, end_expert_id] (inclusive) copy the
+ * token's row to out[src2dst[slot]], multiplied by 1/a1_scales[e-start] when
+ * a1_scales != NULL, cast to out_dtype (f16/bf16/e4m3).  H % 8 == 0. */
+B200MOE_API int b200moe_pre_reorder(const void* x, int x_dtype, void* out, int out_dtype,
+                        const int32_t* src2dst, const int64_t* topk_ids,
+                        const float* a1_scales, int start_expert_id, int end_expert_id,
+                        int64_t T, int topk, int64_t H, void* stream);
+
+/* Fused permute + 1x128 e4m3 activation quantizer: pre_reorder
+ * (moe/group_gemm_kernel.py:81-117) followed by act_quant
+ * (quantization/fp8_kernel.py:33-52) without the [T*k,H] 16-bit round trip.
+ * The token row is quantized once and written to each of its local slots.
+ * out_q rows are out_q_row_stride_bytes apart, out_s rows out_s_row_stride
+ * floats apart, so payload and scales may live in one packed record per row.
+ * H % 128 == 0. */
+B200MOE_API int b200moe_permute_quant_fp8(const void* x, int x_dtype, const int32_t* src2dst,
+                              const int64_t* topk_ids, int start_expert_id, int end_expert_id,
+                              int64_t T, int topk, int64_t H,
+                              void* out_q, int64_t out_q_row_stride_bytes,
+                              float* out_s, int64_t out_s_row_stride, void* stream);
+
+/* silu_and_mul_triton_kernel / gelu_and_mul_triton_kernel
+ * (moe/group_gemm_kernel.py:120-168, 176-235).  gateup [rows, two_I] =
+ * [gate | up]; rows whose reorder_topk_ids is outside [start,end] are skipped
+ * (reorder_topk_ids may be NULL = all rows).  act 0 = silu, 1 = tanh-gelu.
+ * Activation in f32, rounded to the input dtype, product in the input dtype,
+ * times 1/scales[e-start] when scales != NULL, cast to out_dtype. */
+B200MOE_API int b200moe_act_and_mul(const void* gateup, int dtype, void* down_input, int out_dtype,
+                        int64_t rows, int64_t two_I, const int64_t* reorder_topk_ids,
+                        const float* scales, int start_expert_id, int end_expert_id,
+                        int act, void* stream);
+
+/* post_reorder_triton_kernel (moe/group_gemm_kernel.py:238-288) and the
+ * weighted un-permute of moe/all2all_moe.py:270-278:
+ * out[t] = sum over local slots of down_output[src2dst[t,j]] * w[t,j],
+ * accumulated in f32 (as moe/all2all_moe.py:273-277 does), zero when the token
+ * has no local slot.  H % 8 == 0. */
+B200MOE_API int b200moe_post_reorder(const void* down_output, int dtype, void* out,
+                         const int32_t* src2dst, const int64_t* topk_ids,
+                         const float* topk_weights, int start_expert_id, int end_expert_id,
+                         int64_t T, int topk, int64_t H, void* stream);
+
+/* grouped_gemm_triton with block_shape = [128,128]
+ * (moe/group_gemm_kernel.py:442-513; kernel :291-428), fp8 operands.
+ * For every group g, rows [seg_indptr[g], seg_indptr[g+1]) of a use weight
+ * b[weight_indices[g]] ([N,K] e4m3, K-major = weight_column_major) and scales
+ * b_s[weight_indices[g]] ([N/128, K/128] f32); acc += dot_kb * a_s * b_s per
+ * K block.  a [M_total, K] e4m3 with row stride a_row_stride_bytes, a_s
+ * [M_total, K/128] f32 with row stride a_s_row_stride (floats).
+ * seg_indptr / weight_indices are int64 device arrays (weight_indices NULL =
+ * identity).  Unlike the reference the activations arrive already quantized
+ * (the reference quantizes inside the call, :459-469).
+ *
+ * epilogue 0: c [M_total, N] in c_dtype (f32/f16/bf16), row stride N.
+ * epilogue 1: SwiGLU + 1x128 e4m3 re-quantization fused (replaces
+ *   silu_and_mul_triton_kernel :120-168 plus the act_quant of the second
+ *   grouped_gemm_triton call).  b rows [0,N/2) are gate, [N/2,N) are up
+ *   (moe/moe_numerical_equivalence_validation.py:87-88); c is e4m3
+ *   [M_total, N/2] with row stride c_row_stride_bytes and c_s f32
+ *   [M_total, N/2/128] with row stride c_s_row_stride.  Intermediates are
+ *   rounded to bf16 where the reference rounds to its activation dtype.
+ * Rows outside every group are not written.  K % 128 == 0, N % 128 == 0
+ * (epilogue 1: N % 256 == 0).  status_word (may be NULL): a device int32 that
+ * receives B200MOE_DEVICE_TIMEOUT if a bounded wait inside the kernel expires. */
+B200MOE_API int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_bytes,
+                             const float* a_s, int64_t a_s_row_stride,
+                             const void* b, const float* b_s,
+                             void* c, int c_dtype, int64_t c_row_stride_bytes,
+                             float* c_s, int64_t c_s_row_stride,
+                             int64_t M_total, int64_t N, int64_t K,
+                             int num_groups, int num_weights,
+                             const int64_t* seg_indptr, const int64_t* weight_indices,
+                             int epilogue, int32_t* status_word, void* stream);
+
+/* ========================= quantization/bitpack.py ======================== */
+
+/* pack_weights_over_rows / _cols (quantization/bitpack.py:9-67, 84-149,
+ * 228-293): fields of nbits (1,2,4,8) packed little-end-first into words of
+ * width bits (8,16,32).  over_rows != 0: out [R/e, C], word r field i =
+ * w[e*r+i, c]; else out [R, C/e], word c field i = w[r, e*c+i]; e = width/nbits.
+ * w is uint8 [R, C]. */
+B200MOE_API int b200moe_pack_bits(const uint8_t* w, void* out, int64_t R, int64_t C,
+                      int nbits, int width, int over_rows, void* stream);
+/* unpack_over_rows / _cols (quantization/bitpack.py:152-226, 296-373): inverse
+ * of the above into uint8 [R, C]. */
+B200MOE_API int b200moe_unpack_bits(const void* packed, uint8_t* out, int64_t R, int64_t C,
+                        int nbits, int width, int over_rows, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200MOE_H_ */

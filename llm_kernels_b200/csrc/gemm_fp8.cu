@@ -1,0 +1,452 @@
+// fp8 (e4m3) blockwise-scaled GEMMs on the 5th-generation tensor cores.
+//
+//   dense    fp8_gemm             quantization/fp8_kernel.py:108-190
+//   grouped  grouped_gemm_triton  moe/group_gemm_kernel.py:291-513 (block_shape=[128,128])
+//
+// Semantics (both): for every 128-wide K block kb
+//     acc[m,n] += dot_kb(a[m,:], b[n,:]) * a_s[m,kb] * b_s[n/128,kb]
+// The f32 scales are not a hardware block-scale format, so the promotion is done
+// by CUDA cores: the tensor core produces the unscaled dot of one K block into a
+// TMEM stage, epilogue warps read it back (tcgen05.ld) and FMA it into register
+// accumulators while the tensor core fills the other TMEM stage.
+//
+// One persistent CTA per SM, 320 threads:
+//   warp 0     TMA producer: A tile 128x128 B, B tile 256x128 B per K block
+//              (two 128-row boxes: gate rows + up rows for the SwiGLU epilogue,
+//              or two consecutive N blocks otherwise), 4-stage ring
+//   warp 1     owns TMEM (512 columns = 2 stages x 256 f32 columns), issues
+//              4 x tcgen05.mma.kind::f8f6f4 (M128 N256 K32) per K block
+//   warps 2-9  promotion + epilogue; warp w reads TMEM lanes 32*(w%4)..+31 and
+//              64 gate + 64 up (or 64 + 64 plain) columns -> 128 accumulators
+// Tiles are (group, m-tile, n-tile) with n fastest, so CTAs running together
+// share an A tile and walk one expert's weights once through L2.
+//
+// Every wait is a bounded mbarrier wait; on expiry the kernel drains, frees TMEM,
+// writes B200MOE_DEVICE_TIMEOUT to the status word and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace b200moe {
+
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;
+constexpr int kEpiWarps = 8;
+constexpr int kThreads = 64 + kEpiWarps * 32;
+constexpr uint32_t kABytes = BM * BK;
+constexpr uint32_t kBBytes = BN * BK;
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr int kMaxGroups = 2048;
+constexpr uint32_t kTmemCols = 512;
+
+struct SharedTail {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[kAccStages];
+  uint64_t tmem_empty[kAccStages];
+  uint64_t amax_bar[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  float amax[2][2][BM];          // [buffer][column half][row]
+  int32_t seg[kMaxGroups + 1];   // row offsets of the groups
+  int32_t pref[kMaxGroups + 1];  // exclusive prefix of m-tiles per group
+};
+constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(SharedTail);
+
+struct GemmParams {
+  const float* a_s; int64_t a_s_stride;
+  const float* b_s;
+  void* c; int64_t c_stride;          // bytes
+  float* c_s; int64_t c_s_stride;     // floats
+  const int64_t* seg; const int64_t* widx;
+  int64_t M_total;
+  int N, K, num_groups, num_weights, c_dtype, swiglu;
+  int32_t* status;
+};
+
+struct Tile { int m0, m_end, expert, nt; };
+
+__device__ __forceinline__ Tile decode_tile(const SharedTail* sh, const GemmParams& p, int t,
+                                            int num_n_tiles) {
+  const int mt = t / num_n_tiles;
+  int lo = 0, hi = p.num_groups;           // last g with pref[g] <= mt
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (sh->pref[mid] <= mt) lo = mid; else hi = mid;
+  }
+  Tile tl;
+  tl.m0 = sh->seg[lo] + (mt - sh->pref[lo]) * BM;
+  tl.m_end = sh->seg[lo + 1];
+  tl.expert = p.widx ? static_cast<int>(p.widx[lo]) : lo;
+  tl.nt = t - mt * num_n_tiles;
+  return tl;
+}
+
+template <typename T>
+__device__ __forceinline__ void store_row64(T* dst, const float* v);
+template <>
+__device__ __forceinline__ void store_row64<float>(float* dst, const float* v) {
+#pragma unroll
+  for (int j = 0; j < 64; j += 4)
+    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+}
+template <>
+__device__ __forceinline__ void store_row64<__nv_bfloat16>(__nv_bfloat16* dst, const float* v) {
+#pragma unroll
+  for (int j = 0; j < 64; j += 8) {
+    uint4 r;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[j + 2 * i], v[j + 2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst + j) = r;
+  }
+}
+template <>
+__device__ __forceinline__ void store_row64<__half>(__half* dst, const float* v) {
+#pragma unroll
+  for (int j = 0; j < 64; j += 8) {
+    uint4 r;
+    __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[j + 2 * i], v[j + 2 * i + 1]);
+    *reinterpret_cast<uint4*>(dst + j) = r;
+  }
+}
+
+__device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  SharedTail* sh = reinterpret_cast<SharedTail*>(smem + size_t(kStages) * kStageBytes);
+  volatile int* abort_flag = &sh->abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int KB = p.K / BK;
+  const int NB = p.N / 128;
+  const int num_n_tiles = p.swiglu ? (p.N / 2) / 128 : (p.N + BN - 1) / BN;
+
+  // ---- setup: barriers, TMEM, group table -----------------------------------------
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&sh->full[s], 1); ptx::mbar_init(&sh->empty[s], 1); }
+    for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&sh->tmem_full[s], 1); ptx::mbar_init(&sh->tmem_empty[s], kEpiWarps); }
+    ptx::mbar_init(&sh->amax_bar[0], kEpiWarps);
+    ptx::mbar_init(&sh->amax_bar[1], kEpiWarps);
+    sh->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensormap(&tmap_a);
+    ptx::prefetch_tensormap(&tmap_b);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&sh->tmem_base, kTmemCols);
+    ptx::tmem_relinquish();
+  }
+  // group row offsets
+  for (int g = threadIdx.x; g <= p.num_groups; g += kThreads)
+    sh->seg[g] = p.seg ? static_cast<int32_t>(p.seg[g]) : (g == 0 ? 0 : static_cast<int32_t>(p.M_total));
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  ptx::tc_fence_after_sync();
+  if (warp == 2) {  // exclusive prefix of m-tiles per group, 32 groups per step
+    int run = 0;
+    for (int g0 = 0; g0 < p.num_groups; g0 += 32) {
+      const int g = g0 + lane;
+      int v = 0;
+      if (g < p.num_groups) { const int m = sh->seg[g + 1] - sh->seg[g]; v = m > 0 ? (m + BM - 1) / BM : 0; }
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
+      if (g < p.num_groups) sh->pref[g] = run + incl - v;
+      run += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) sh->pref[p.num_groups] = run;
+  }
+  __syncthreads();
+  const uint32_t tmem_base = sh->tmem_base;
+  const int total_tiles = sh->pref[p.num_groups] * num_n_tiles;
+
+  if (warp == 0) {
+    // ================================ TMA producer ================================
+    if (lane == 0) {
+      int stage = 0; uint32_t phase = 0;
+      uint32_t armed = 0, armed_parity = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        const Tile tl = decode_tile(sh, p, t, num_n_tiles);
+        const int brow0 = tl.expert * p.N + (p.swiglu ? tl.nt * 128 : tl.nt * BN);
+        const int brow1 = p.swiglu ? tl.expert * p.N + p.N / 2 + tl.nt * 128 : brow0 + 128;
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!ptx::mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + size_t(stage) * kStageBytes;
+          uint8_t* sb = sa + kABytes;
+          ptx::mbar_arrive_expect_tx(&sh->full[stage], kStageBytes);
+          armed |= 1u << stage;
+          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+          ptx::tma_load_2d(sa, &tmap_a, &sh->full[stage], kb * BK, tl.m0);
+          ptx::tma_load_2d(sb, &tmap_b, &sh->full[stage], kb * BK, brow0);
+          ptx::tma_load_2d(sb + kBBytes / 2, &tmap_b, &sh->full[stage], kb * BK, brow1);
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if (!ok) {
+        // leave no bulk copy in flight behind us: wait (bounded) for every armed stage
+        for (int s = 0; s < kStages; ++s) {
+          if (!((armed >> s) & 1u)) continue;
+          const uint64_t t0 = ptx::global_timer_ns();
+          while (!ptx::mbar_try_wait(&sh->full[s], (armed_parity >> s) & 1u) &&
+                 ptx::global_timer_ns() - t0 < 20000000ull) {}
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ================================ MMA issuer ==================================
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::umma_idesc(1, 0, 0, BM, BN);
+      int stage = 0; uint32_t phase = 0;
+      int as = 0; uint32_t aphase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        for (int kb = 0; kb < KB; ++kb) {
+          if (!ptx::mbar_wait(&sh->full[stage], phase, abort_flag)) { ok = false; break; }
+          if (!ptx::mbar_wait(&sh->tmem_empty[as], aphase ^ 1u, abort_flag)) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          const uint32_t sa = ptx::smem_u32(smem + size_t(stage) * kStageBytes);
+          const uint64_t adesc = ptx::umma_desc_sw128(sa);
+          const uint64_t bdesc = ptx::umma_desc_sw128(sa + kABytes);
+          const uint32_t d = tmem_base + static_cast<uint32_t>(as) * BN;
+#pragma unroll
+          for (int k = 0; k < BK / 32; ++k)   // +32 bytes along K = +2 in the >>4 address field
+            ptx::umma_f8f6f4(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+          ptx::umma_commit(&sh->empty[stage]);      // smem slot reusable once the MMAs retire
+          ptx::umma_commit(&sh->tmem_full[as]);     // K-block product ready for promotion
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+        }
+      }
+    }
+  } else {
+    // ========================= promotion + epilogue warps ==========================
+    const int e = warp - 2;
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int hsel = e >> 2;             // which 64-column half of each 128-column block
+    const int r_in_tile = q * 32 + lane;
+    const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
+    int as = 0; uint32_t aphase = 0;
+    int it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+      const Tile tl = decode_tile(sh, p, t, num_n_tiles);
+      const int row = tl.m0 + r_in_tile;
+      const int64_t row_ld = min(static_cast<int64_t>(row), p.M_total - 1);
+      const int nb0 = p.swiglu ? tl.nt : min(tl.nt * 2, NB - 1);
+      const int nb1 = p.swiglu ? NB / 2 + tl.nt : min(tl.nt * 2 + 1, NB - 1);
+      const float* as_ptr = p.a_s + row_ld * p.a_s_stride;
+      const float* bs0_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb0) * KB;
+      const float* bs1_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb1) * KB;
+      float acc[128];
+#pragma unroll
+      for (int j = 0; j < 128; ++j) acc[j] = 0.f;
+      float sa_n = __ldg(as_ptr), b0_n = __ldg(bs0_ptr), b1_n = __ldg(bs1_ptr);
+      for (int kb = 0; kb < KB; ++kb) {
+        const float s0 = sa_n * b0_n, s1 = sa_n * b1_n;
+        if (kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
+        if (!ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after_sync();
+        const uint32_t tcol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const float sc = half == 0 ? s0 : s1;
+#pragma unroll
+          for (int c = 0; c < 4; c += 2) {
+            uint32_t r0[16], r1[16];
+            ptx::tmem_ld16(tcol + half * 128 + c * 16, r0);
+            ptx::tmem_ld16(tcol + half * 128 + (c + 1) * 16, r1);
+            ptx::tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              acc[half * 64 + c * 16 + j] = fmaf(__uint_as_float(r0[j]), sc, acc[half * 64 + c * 16 + j]);
+              acc[half * 64 + (c + 1) * 16 + j] = fmaf(__uint_as_float(r1[j]), sc, acc[half * 64 + (c + 1) * 16 + j]);
+            }
+          }
+        }
+        ptx::tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&sh->tmem_empty[as]);
+        if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+      }
+      if (!ok) break;
+      const bool row_ok = row < tl.m_end;
+      if (!p.swiglu) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int col0 = tl.nt * BN + half * 128 + hsel * 64;
+          if (row_ok && col0 < p.N) {
+            uint8_t* dst = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(row) * p.c_stride;
+            if (p.c_dtype == B200MOE_BF16) store_row64(reinterpret_cast<__nv_bfloat16*>(dst) + col0, acc + half * 64);
+            else if (p.c_dtype == B200MOE_F16) store_row64(reinterpret_cast<__half*>(dst) + col0, acc + half * 64);
+            else store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
+          }
+        }
+      } else {
+        // SwiGLU with the reference's roundings (gate/up GEMM output, silu and the
+        // product each rounded to bf16), then 1x128 e4m3 quantization of the row block.
+        float amax = 0.f;
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float g = bf16r(acc[j]);
+          const float u = bf16r(acc[64 + j]);
+          const float a = bf16r(g * __fdividef(1.0f, 1.0f + __expf(-g)));
+          const float h = bf16r(a * u);
+          acc[j] = h;
+          amax = fmaxf(amax, fabsf(h));
+        }
+        const int buf = it & 1;
+        sh->amax[buf][hsel][r_in_tile] = amax;
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&sh->amax_bar[buf]);
+        if (!ptx::mbar_wait(&sh->amax_bar[buf], (it >> 1) & 1u, abort_flag)) { ok = false; break; }
+        amax = fmaxf(amax, sh->amax[buf][hsel ^ 1][r_in_tile]);
+        if (row_ok) {
+          const float scale = __fdiv_rn(amax, 448.f);
+          uint8_t* dst = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(row) * p.c_stride + tl.nt * 128 + hsel * 64;
+#pragma unroll
+          for (int j = 0; j < 64; j += 16) {
+            float q0[8], q1[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { q0[i] = __fdiv_rn(acc[j + i], scale); q1[i] = __fdiv_rn(acc[j + 8 + i], scale); }
+            const uint2 lo = pack8_e4m3(q0), hi = pack8_e4m3(q1);
+            *reinterpret_cast<uint4*>(dst + j) = make_uint4(lo.x, lo.y, hi.x, hi.y);
+          }
+          if (hsel == 0) p.c_s[static_cast<int64_t>(row) * p.c_s_stride + tl.nt] = scale;
+        }
+      }
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------------
+  ptx::tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if (threadIdx.x == 0 && sh->abort_flag && p.status) *p.status = B200MOE_DEVICE_TIMEOUT;
+}
+
+// ---- host side ---------------------------------------------------------------------------
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+static EncodeFn get_encode() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+// rows x cols bytes, row stride in bytes, box 128 rows x 128 bytes, 128-byte swizzle.
+static int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
+                       uint64_t row_stride) {
+  EncodeFn enc = get_encode();
+  if (!enc) return fail(B200MOE_UNSUPPORTED_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride};
+  const cuuint32_t box[2] = {128, 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200MOE_BAD_ARG, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return B200MOE_OK;
+}
+
+static int sm_count_and_check(int* sms) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(B200MOE_UNSUPPORTED_DEVICE, "no CUDA device");
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev);
+  if (major != 10) return fail(B200MOE_UNSUPPORTED_DEVICE, "tcgen05 kernels need compute capability 10.x, device has %d.x", major);
+  return B200MOE_OK;
+}
+
+static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParams p, int64_t tiles_hint,
+                       cudaStream_t st) {
+  int sms = 0;
+  if (int rc = sm_count_and_check(&sms)) return rc;
+  CUtensorMap ma, mb;
+  if (int rc = make_map_u8(&ma, a, static_cast<uint64_t>(p.M_total), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_stride))) return rc;
+  if (int rc = make_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.K))) return rc;
+  cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  int grid = sms;
+  if (tiles_hint > 0 && tiles_hint < grid) grid = static_cast<int>(tiles_hint);
+  gemm_fp8_block_kernel<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, p);
+  return check_launch("gemm_fp8_block");
+}
+
+}  // namespace b200moe
+
+using namespace b200moe;
+
+extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const void* b,
+                                      const float* b_s, void* c, int c_dtype, int64_t M,
+                                      int64_t N, int64_t K, void* stream) {
+  B200MOE_REQUIRE(a && a_s && b && b_s && c, B200MOE_BAD_ARG, "gemm_fp8_block: null pointer");
+  B200MOE_REQUIRE(M >= 0 && M < (int64_t(1) << 31) && N > 0 && K > 0 && K % 128 == 0 && N % 128 == 0 && N * K < (int64_t(1) << 40),
+                  B200MOE_BAD_SHAPE, "gemm_fp8_block: M=%lld N=%lld K=%lld (N and K must be multiples of 128)",
+                  (long long)M, (long long)N, (long long)K);
+  B200MOE_REQUIRE(c_dtype == B200MOE_F32 || c_dtype == B200MOE_F16 || c_dtype == B200MOE_BF16, B200MOE_BAD_DTYPE,
+                  "gemm_fp8_block: c dtype %d", c_dtype);
+  B200MOE_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(c, 16), B200MOE_BAD_ALIGN,
+                  "gemm_fp8_block: Input tensors must be 16-byte aligned");
+  if (M == 0) return B200MOE_OK;
+  const int esz = c_dtype == B200MOE_F32 ? 4 : 2;
+  GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
+               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr};
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  return launch_gemm(a, K, b, p, tiles, as_stream(stream));
+}
+
+extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_bytes, const float* a_s,
+                                        int64_t a_s_row_stride, const void* b, const float* b_s,
+                                        void* c, int c_dtype, int64_t c_row_stride_bytes, float* c_s,
+                                        int64_t c_s_row_stride, int64_t M_total, int64_t N, int64_t K,
+                                        int num_groups, int num_weights, const int64_t* seg_indptr,
+                                        const int64_t* weight_indices, int epilogue,
+                                        int32_t* status_word, void* stream) {
+  B200MOE_REQUIRE(a && a_s && b && b_s && c && seg_indptr, B200MOE_BAD_ARG, "grouped_gemm_fp8: null pointer");
+  B200MOE_REQUIRE(epilogue == 0 || epilogue == 1, B200MOE_BAD_ARG, "grouped_gemm_fp8: epilogue %d", epilogue);
+  B200MOE_REQUIRE(M_total >= 0 && M_total < (int64_t(1) << 31) && N > 0 && K > 0 && K % 128 == 0 && N % 128 == 0,
+                  B200MOE_BAD_SHAPE, "grouped_gemm_fp8: M=%lld N=%lld K=%lld (N and K must be multiples of 128)",
+                  (long long)M_total, (long long)N, (long long)K);
+  B200MOE_REQUIRE(num_groups >= 1 && num_groups <= kMaxGroups && num_weights >= 1 &&
+                  static_cast<int64_t>(num_weights) * N < (int64_t(1) << 31),
+                  B200MOE_BAD_SHAPE, "grouped_gemm_fp8: num_groups=%d (max %d) num_weights=%d", num_groups, kMaxGroups, num_weights);
+  B200MOE_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(c, 16) && a_row_stride_bytes % 16 == 0 &&
+                  a_row_stride_bytes >= K && c_row_stride_bytes % 16 == 0,
+                  B200MOE_BAD_ALIGN, "grouped_gemm_fp8: pointers and row strides must be 16-byte aligned");
+  B200MOE_REQUIRE(a_s_row_stride >= K / 128, B200MOE_BAD_ARG, "grouped_gemm_fp8: a_s row stride too small");
+  if (epilogue == 1) {
+    B200MOE_REQUIRE(N % 256 == 0, B200MOE_BAD_SHAPE, "grouped_gemm_fp8: the SwiGLU epilogue needs N %% 256 == 0, got %lld", (long long)N);
+    B200MOE_REQUIRE(c_dtype == B200MOE_FP8_E4M3 && c_s && c_row_stride_bytes >= N / 2 && c_s_row_stride >= N / 256,
+                    B200MOE_BAD_ARG, "grouped_gemm_fp8: the SwiGLU epilogue writes e4m3 rows and f32 scales");
+  } else {
+    B200MOE_REQUIRE(c_dtype == B200MOE_F32 || c_dtype == B200MOE_F16 || c_dtype == B200MOE_BF16, B200MOE_BAD_DTYPE,
+                    "grouped_gemm_fp8: c dtype %d", c_dtype);
+    B200MOE_REQUIRE(c_row_stride_bytes >= N * (c_dtype == B200MOE_F32 ? 4 : 2), B200MOE_BAD_ARG, "grouped_gemm_fp8: c row stride too small");
+  }
+  if (M_total == 0) return B200MOE_OK;
+  GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
+               weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
+               num_weights, c_dtype, epilogue, status_word};
+  return launch_gemm(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+}

@@ -1,0 +1,216 @@
+"""Expert-parallel quantized MoE layer with the call surface of the reference's
+moe/all2all_moe.py: ``MoEGate(config).forward(h) -> (topk_idx, topk_weight)`` (:60-118)
+and ``DeepseekV3MoE(config).forward(hidden_states[B,S,H]) -> [B,S,H]`` (:167-184).
+
+Where the reference runs a per-expert Python loop (``moe_infer``, :186-280) and leaves
+its fused path as a stub (``triton_group_gemm_moe_infer``, :282-286), this module runs
+one fused pipeline of sm_100a kernels:
+
+    router_topk -> route_metadata -> permute + 1x128 e4m3 quantize
+      -> [all-to-all-v dispatch of fp8 rows + scales, one packed record per row]
+      -> grouped GEMM-1 (tcgen05) with SwiGLU + re-quantize in the epilogue
+      -> grouped GEMM-2 (tcgen05)
+      -> [all-to-all-v combine, bf16 rows]
+      -> routing-weighted un-permute (f32 accumulate)
+
+Experts are sharded as in the reference (:130-147): rank r owns experts
+[r*E/ep, (r+1)*E/ep).  Expert weights live in the fused layout of the reference's
+grouped path (moe/sglang_moe_all_gather_all_reduce.py:208-264): w13 [E_l, 2I, H] =
+[gate ; up], w2 [E_l, H, I], both e4m3 with f32 128x128 block scales.
+"""
+import math
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+from torch import nn
+
+from .. import _native as N
+from ..quantization import fp8_kernel
+from . import ep_comm
+from . import group_gemm_kernel as G
+from .config import Config  # noqa: F401  (re-exported like the reference does)
+from .utils import ResultCollector  # noqa: F401
+
+
+class MoEGate(nn.Module):
+    """Router (reference :31-118): f32 logits, sigmoid (or softmax) scores, optional
+    e_score_correction_bias, group-limited top-k, renormalisation, scaling."""
+
+    def __init__(self, config):
+        super().__init__()
+        self.config = config
+        self.top_k = config.num_experts_per_tok
+        self.n_routed_experts = config.n_routed_experts
+        self.routed_scaling_factor = config.routed_scaling_factor
+        self.scoring_func = config.scoring_func
+        self.topk_method = config.topk_method
+        self.n_group = config.n_group
+        self.topk_group = config.topk_group
+        self.norm_topk_prob = config.norm_topk_prob
+        self.gating_dim = config.hidden_size
+        self.weight = nn.Parameter(torch.empty((self.n_routed_experts, self.gating_dim), dtype=torch.float32))
+        if self.topk_method == "noaux_tc":
+            self.e_score_correction_bias = nn.Parameter(torch.zeros((self.n_routed_experts), dtype=torch.float32))
+        self.reset_parameters()
+
+    def reset_parameters(self) -> None:
+        nn.init.kaiming_uniform_(self.weight, a=math.sqrt(5))
+
+    @torch.no_grad()
+    def forward(self, hidden_states):
+        if self.scoring_func not in ("sigmoid", "softmax"):
+            raise NotImplementedError(f"insupportable scoring function for MoE gating: {self.scoring_func}")
+        if self.topk_method != "noaux_tc":
+            raise NotImplementedError(f"insupportable TopK function for MoE gating: {self.topk_method}")
+        assert not self.training
+        h = hidden_states.shape[-1]
+        x = hidden_states.reshape(-1, h)
+        N.require_cuda(x, self.weight)
+        if not x.is_contiguous():
+            x = x.contiguous()
+        T = x.shape[0]
+        topk_idx = torch.empty((T, self.top_k), dtype=torch.int64, device=x.device)
+        topk_weight = torch.empty((T, self.top_k), dtype=torch.float32, device=x.device)
+        w = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
+        bias = self.e_score_correction_bias
+        bias = bias if bias.dtype == torch.float32 else bias.float()
+        N.check(N.lib().b200moe_router_topk(
+            N.ptr(x), N.dtype_code(x.dtype), N.ptr(w), N.ptr(bias), T, h, self.n_routed_experts,
+            self.top_k, self.n_group, self.topk_group, 0 if self.scoring_func == "sigmoid" else 1,
+            1 if self.norm_topk_prob else 0, float(self.routed_scaling_factor),
+            N.ptr(topk_idx), N.ptr(topk_weight), N.stream()))
+        return topk_idx, topk_weight
+
+
+class DeepseekV3MoE(nn.Module):
+    """A mixed expert module (reference :120-286) over quantized fused expert weights."""
+
+    def __init__(self, config, device=None):
+        super().__init__()
+        self.config = config
+        self.num_experts_per_tok = config.num_experts_per_tok
+        if getattr(config, "quantize_method", "fp8_block") != "fp8_block":
+            raise NotImplementedError(f"quantize_method {config.quantize_method!r}")
+        if getattr(config, "hidden_act", "silu") != "silu":
+            raise NotImplementedError("the fused GEMM-1 epilogue implements silu")
+        if hasattr(config, "ep_size") and config.ep_size > 1:
+            assert config.ep_size == dist.get_world_size()
+            self.ep_size = config.ep_size
+            self.ep_rank = dist.get_rank()
+        else:
+            self.ep_size, self.ep_rank = 1, 0
+        E, H, I = config.n_routed_experts, config.hidden_size, config.moe_intermediate_size
+        assert E % self.ep_size == 0
+        assert H % 128 == 0 and I % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
+        self.experts_per_rank = E // self.ep_size
+        El = self.experts_per_rank
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        f8 = torch.float8_e4m3fn
+        reg = lambda name, t: self.register_buffer(name, t, persistent=True)
+        reg("w13_weight", torch.zeros(El, 2 * I, H, dtype=f8, device=dev))
+        reg("w13_weight_scale", torch.ones(El, 2 * I // 128, H // 128, dtype=torch.float32, device=dev))
+        reg("w2_weight", torch.zeros(El, H, I, dtype=f8, device=dev))
+        reg("w2_weight_scale", torch.ones(El, H // 128, I // 128, dtype=torch.float32, device=dev))
+        self.gate = MoEGate(config).to(dev)
+        if config.n_shared_experts:
+            raise NotImplementedError("shared experts are not built yet")
+        self._buffers_cache = {}
+        self._status = torch.zeros(1, dtype=torch.int32, device=dev)
+        self.last_recv_rows = None
+
+    # ---- weights ---------------------------------------------------------------------
+    @torch.no_grad()
+    def load_expert(self, local_idx: int, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor):
+        """Quantizes one expert's nn.Linear weights (gate/up [I,H], down [H,I], the layout of
+        DeepseekV3MLP, reference :13-29) into the fused e4m3 tensors."""
+        w13 = torch.cat([gate_w, up_w], dim=0).contiguous()
+        q, s = fp8_kernel.weight_quant(w13)
+        self.w13_weight[local_idx].copy_(q)
+        self.w13_weight_scale[local_idx].copy_(s)
+        q, s = fp8_kernel.weight_quant(down_w.contiguous())
+        self.w2_weight[local_idx].copy_(q)
+        self.w2_weight_scale[local_idx].copy_(s)
+
+    def _buf(self, name, shape, dtype):
+        key = name
+        t = self._buffers_cache.get(key)
+        n = 1
+        for d in shape:
+            n *= d
+        if t is None or t.dtype != dtype or t.numel() < n:
+            t = torch.empty(max(n, 1), dtype=dtype, device=self.w13_weight.device)
+            self._buffers_cache[key] = t
+        return t[:n].view(*shape)
+
+    # ---- forward ---------------------------------------------------------------------
+    @torch.no_grad()
+    def forward(self, hidden_states):
+        orig_shape = hidden_states.shape
+        topk_idx, topk_weight = self.gate(hidden_states)
+        x = hidden_states.reshape(-1, orig_shape[-1])
+        if not x.is_contiguous():
+            x = x.contiguous()
+        y = self.triton_group_gemm_moe_infer(x, topk_idx, topk_weight)
+        return y.view(*orig_shape)
+
+    # the reference's unfused entry point routes to the same pipeline
+    def moe_infer(self, x, topk_ids, topk_weight):
+        return self.triton_group_gemm_moe_infer(x, topk_ids, topk_weight)
+
+    @torch.no_grad()
+    def triton_group_gemm_moe_infer(self, x, topk_ids, topk_weight):
+        """The fused expert-parallel pipeline (finishes the stub at reference :282-286)."""
+        cfg = self.config
+        T, H = x.shape
+        k = topk_ids.shape[1]
+        I = cfg.moe_intermediate_size
+        E = cfg.n_routed_experts
+        S = T * k
+        assert x.dtype == torch.bfloat16, "activations must be bfloat16"
+        reorder_ids, src2dst, seg_indptr = G.run_moe_ep_preproess(topk_ids, E)
+        # packed record: e4m3 row + f32 scales, padded so rows stay 16-byte aligned for TMA
+        rec = (H + (H // 128) * 4 + 15) // 16 * 16
+        send = self._buf("send", (S, rec), torch.uint8)
+        send_q = send[:, :H]
+        send_s = send[:, H:H + (H // 128) * 4].view(torch.float32)
+        G.permute_quant_fp8(x, src2dst, topk_ids, 0, E - 1, send_q, send_s)
+
+        if self.ep_size == 1:
+            a_q, a_s, rows = send_q, send_s, S
+            seg, widx = seg_indptr, None
+        else:
+            # Received rows stay ordered by (source rank, local expert); each such run is one
+            # GEMM group that reaches its expert through weight_indices, so the reference's
+            # host-side re-sort (:229-240) is not needed.
+            plan = ep_comm.plan_exchange(seg_indptr, self.ep_size)
+            rows = plan.recv_rows
+            recv = self._buf("recv", (max(rows, 1), rec), torch.uint8)[:rows]
+            ep_comm.dispatch(plan, send, recv)
+            a_q, a_s = recv[:, :H], recv[:, H:H + (H // 128) * 4].view(torch.float32)
+            seg, widx = plan.seg_indptr, plan.weight_indices
+        self.last_recv_rows = rows
+
+        h_q = self._buf("h_q", (rows, I), torch.uint8)
+        h_s = self._buf("h_s", (rows, I // 128), torch.float32)
+        down = self._buf("down", (rows, H), torch.bfloat16)
+        if rows > 0:
+            G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx,
+                               h_q, h_s, epilogue=1, status_word=self._status)
+            G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
+                               down, None, epilogue=0, status_word=self._status)
+
+        if self.ep_size > 1:
+            back = self._buf("back", (S, H), torch.bfloat16)
+            down = ep_comm.combine(plan, down, back)
+        out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+        G.post_reorder_triton_kernel[(T,)](down, out, src2dst, topk_ids, topk_weight, 0, E - 1, k, H,
+                                           BLOCK_SIZE=512)
+        return out
+
+    def check_status(self):
+        """Raises if a kernel of an earlier forward reported a device-side timeout (synchronises)."""
+        s = int(self._status.item())
+        if s:
+            self._status.zero_()
+            raise N.B200MoeError(s, "a bounded device-side wait expired inside a grouped GEMM")

@@ -1,0 +1,37 @@
+"""Layer configuration; attribute names follow the reference's moe/config.py:3-31.
+
+Two attributes gain values the reference rejects: scoring_func may be "softmax"
+(the reference raises NotImplementedError for anything but "sigmoid",
+moe/all2all_moe.py:67-72) and quantize_method selects the B200 expert path.
+"""
+import torch
+
+
+class Config:
+    def __init__(self):
+        self.hidden_size = 7168
+        self.intermediate_size = 18432
+        self.num_experts_per_tok = 8
+        self.n_routed_experts = 256
+        self.routed_scaling_factor = 2.5
+        self.scoring_func = "sigmoid"          # or "softmax"
+        self.seq_aux = True
+        self.topk_method = "noaux_tc"
+        self.n_group = 8
+        self.topk_group = 4
+        self.norm_topk_prob = True
+        self.moe_intermediate_size = 2048
+        self.n_shared_experts = 0
+        self.ep_size = 1
+        self.hidden_act = "silu"
+        self.use_triton_group_gemm = True      # the grouped path is the only path here
+
+        # quantization: "fp8_block" = e4m3 weights with 128x128 scales, e4m3 activations 1x128
+        self.quantize_method = "fp8_block"
+        self.use_block_quant = True
+        self.w_quant_block_size = (128, 128)
+        self.a_quant_block_size = (1, 128)
+        self.w_bit = 8
+        self.a_bit = 8
+        self.w_dtype = torch.float8_e4m3fn
+        self.a_dtype = torch.float8_e4m3fn

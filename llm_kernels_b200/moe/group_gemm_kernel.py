@@ -1,0 +1,175 @@
+"""Grouped-GEMM MoE operators with the call surface of the reference's
+moe/group_gemm_kernel.py, implemented by sm_100a CUDA kernels.
+
+The reference launches its Triton kernels as ``kernel[(grid,)](args, BLOCK_SIZE=...)``
+(e.g. moe/sglang_moe_all_gather_all_reduce.py:312, 375, 429).  The objects
+exported here accept the same syntax; the grid and BLOCK_SIZE are ignored because
+the CUDA launchers size themselves.
+"""
+from typing import List, Optional
+
+import torch
+
+from .. import _native as N
+
+_workspaces = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    key = (device, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(max(nbytes, 1 << 16), dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def run_moe_ep_preproess(topk_ids: torch.Tensor, num_experts: int):
+    """Stable sort of the flat expert ids (reference :48-78).
+
+    Returns (reorder_topk_ids int64 [T*k], src2dst int32 [T*k], seg_indptr int64 [E+1])."""
+    N.require_cuda(topk_ids)
+    assert topk_ids.dtype == torch.int64, "topk_ids must be int64"
+    flat = topk_ids.contiguous().view(-1)
+    n = flat.numel()
+    dev = flat.device
+    reorder_topk_ids = torch.empty(n, dtype=torch.int64, device=dev)
+    src2dst = torch.empty(n, dtype=torch.int32, device=dev)
+    seg_indptr = torch.empty(num_experts + 1, dtype=torch.int64, device=dev)
+    need = N.lib().b200moe_route_metadata_workspace_bytes(n, num_experts)
+    ws = _workspace(dev, need)
+    N.check(N.lib().b200moe_route_metadata(N.ptr(flat), n, num_experts, N.ptr(reorder_topk_ids), N.ptr(src2dst),
+                                           N.ptr(seg_indptr), N.ptr(ws), ws.numel(), N.stream()))
+    return reorder_topk_ids, src2dst, seg_indptr
+
+
+class _Launcher:
+    """Accepts the Triton launch form ``obj[grid](*args, **meta)``."""
+
+    def __init__(self, fn):
+        self._fn = fn
+        self.__doc__ = fn.__doc__
+        self.__name__ = fn.__name__
+
+    def __getitem__(self, grid):
+        return self._fn
+
+    def __call__(self, *args, **kwargs):
+        return self._fn(*args, **kwargs)
+
+
+def _f32_or_none(t):
+    if t is None:
+        return None
+    return t if t.dtype == torch.float32 else t.float()
+
+
+def _pre_reorder(input_ptr, gateup_input_ptr, src2dst_ptr, topk_ids_ptr, a1_scales_ptr,
+                 start_expert_id, end_expert_id, topk, hidden_size, BLOCK_SIZE=512):
+    """reference :81-117"""
+    N.require_cuda(input_ptr, gateup_input_ptr, src2dst_ptr, topk_ids_ptr)
+    assert input_ptr.is_contiguous() and gateup_input_ptr.is_contiguous()
+    sc = _f32_or_none(a1_scales_ptr)
+    T = input_ptr.numel() // hidden_size
+    N.check(N.lib().b200moe_pre_reorder(N.ptr(input_ptr), N.dtype_code(input_ptr.dtype), N.ptr(gateup_input_ptr),
+                                        N.dtype_code(gateup_input_ptr.dtype), N.ptr(src2dst_ptr), N.ptr(topk_ids_ptr),
+                                        N.ptr(sc), int(start_expert_id), int(end_expert_id), T, int(topk),
+                                        int(hidden_size), N.stream()))
+
+
+def _act_and_mul(act):
+    def run(gateup_output, down_input, hidden_size, reorder_topk_ids, scales, start_expert_id,
+            end_expert_id, BLOCK_SIZE=512):
+        N.require_cuda(gateup_output, down_input)
+        assert gateup_output.is_contiguous() and down_input.is_contiguous()
+        sc = _f32_or_none(scales)
+        rows = gateup_output.numel() // hidden_size
+        N.check(N.lib().b200moe_act_and_mul(N.ptr(gateup_output), N.dtype_code(gateup_output.dtype), N.ptr(down_input),
+                                            N.dtype_code(down_input.dtype), rows, int(hidden_size),
+                                            N.ptr(reorder_topk_ids), N.ptr(sc), int(start_expert_id),
+                                            int(end_expert_id), act, N.stream()))
+    run.__name__ = "silu_and_mul" if act == 0 else "gelu_and_mul"
+    run.__doc__ = "reference :120-168" if act == 0 else "reference :176-235"
+    return run
+
+
+def _post_reorder(down_output_ptr, output_ptr, src2dst_ptr, topk_ids_ptr, topk_weights_ptr,
+                  start_expert_id, end_expert_id, topk, hidden_size, BLOCK_SIZE=512):
+    """reference :238-288 (f32 accumulation)"""
+    N.require_cuda(down_output_ptr, output_ptr)
+    assert down_output_ptr.is_contiguous() and output_ptr.is_contiguous()
+    assert down_output_ptr.dtype == output_ptr.dtype
+    w = _f32_or_none(topk_weights_ptr)
+    T = output_ptr.numel() // hidden_size
+    N.check(N.lib().b200moe_post_reorder(N.ptr(down_output_ptr), N.dtype_code(down_output_ptr.dtype), N.ptr(output_ptr),
+                                         N.ptr(src2dst_ptr), N.ptr(topk_ids_ptr), N.ptr(w), int(start_expert_id),
+                                         int(end_expert_id), T, int(topk), int(hidden_size), N.stream()))
+
+
+pre_reorder_triton_kernel = _Launcher(_pre_reorder)
+silu_and_mul_triton_kernel = _Launcher(_act_and_mul(0))
+gelu_and_mul_triton_kernel = _Launcher(_act_and_mul(1))
+post_reorder_triton_kernel = _Launcher(_post_reorder)
+
+
+def permute_quant_fp8(x, src2dst, topk_ids, start_expert_id, end_expert_id, out_q, out_s):
+    """Fused pre_reorder (:81-117) + 1x128 e4m3 act_quant.  out_q is a 2-D uint8/e4m3 view
+    [S, >=H] and out_s a 2-D f32 view [S, >=H/128]; both may be strided views of one packed
+    record buffer."""
+    N.require_cuda(x, out_q, out_s)
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    assert x.is_contiguous() and out_q.stride(1) == 1 and out_s.stride(1) == 1
+    N.check(N.lib().b200moe_permute_quant_fp8(N.ptr(x), N.dtype_code(x.dtype), N.ptr(src2dst), N.ptr(topk_ids),
+                                              int(start_expert_id), int(end_expert_id), T, k, H,
+                                              N.ptr(out_q), out_q.stride(0) * out_q.element_size(),
+                                              N.ptr(out_s), out_s.stride(0), N.stream()))
+
+
+def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, epilogue: int = 0,
+                     status_word=None):
+    """tcgen05 grouped blockwise GEMM on already-quantized activations.
+    a [M,K] e4m3/uint8 (row-strided view allowed), a_s [M,K/128] f32 (row-strided view allowed),
+    b [W,N,K] e4m3, b_s [W,N/128,K/128] f32, seg_indptr int64 [G+1], weight_indices int64 [G] or
+    None.  epilogue 0: c [M,N] bf16/f16/f32; epilogue 1 (SwiGLU + requant): c [M,N/2] e4m3,
+    c_s [M,N/256] f32."""
+    N.require_cuda(a, a_s, b, b_s, c)
+    assert b.is_contiguous() and b_s.is_contiguous() and a.stride(1) == 1 and a_s.stride(1) == 1
+    assert b_s.dtype == torch.float32 and a_s.dtype == torch.float32
+    M, K = a.shape
+    W, Nn, Kb = b.shape
+    assert Kb == K
+    G = seg_indptr.numel() - 1
+    c_dtype = N.FP8_E4M3 if epilogue == 1 else N.dtype_code(c.dtype)
+    N.check(N.lib().b200moe_grouped_gemm_fp8(
+        N.ptr(a), a.stride(0) * a.element_size(), N.ptr(a_s), a_s.stride(0), N.ptr(b), N.ptr(b_s),
+        N.ptr(c), c_dtype, c.stride(0) * c.element_size(),
+        N.ptr(c_s), 0 if c_s is None else c_s.stride(0), M, Nn, K, G, W,
+        N.ptr(seg_indptr), N.ptr(weight_indices), epilogue, N.ptr(status_word), N.stream()))
+    return c
+
+
+def grouped_gemm_triton(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, batch_size: int,
+                        weight_column_major: bool, seg_indptr: Optional[torch.Tensor] = None,
+                        weight_indices: Optional[torch.Tensor] = None, use_fp8_w8a8: bool = False,
+                        scale_a: torch.Tensor = None, scale_b: torch.Tensor = None,
+                        block_shape: Optional[List[int]] = None):
+    """reference :442-513.  b must be e4m3 with block_shape == [128, 128].  As in the
+    reference, `a` arrives unquantized (f16/bf16) and is quantized 1x128 inside the call
+    (the reference does it with its int8 quantizer, :459-469); pass an e4m3 `a` together
+    with scale_a to skip that."""
+    assert weight_column_major == True  # noqa: E712  (same assert as the reference)
+    assert block_shape is not None and list(block_shape) == [128, 128], "only block_shape=[128,128] is supported"
+    assert b.dtype == torch.float8_e4m3fn, "the B200 grouped GEMM takes e4m3 weights"
+    assert seg_indptr is not None
+    if a.dtype != torch.float8_e4m3fn:
+        from ..quantization.fp8_kernel import act_quant
+        a, scale_a = act_quant(a.contiguous(), block_shape[1])
+    assert scale_a is not None and scale_b is not None
+    assert -(-a.shape[-1] // block_shape[1]) == scale_a.shape[-1]
+    assert -(-b.shape[-2] // block_shape[0]) == scale_b.shape[-2]
+    assert -(-b.shape[-1] // block_shape[1]) == scale_b.shape[-1]
+    seg = seg_indptr if seg_indptr.is_contiguous() else seg_indptr.contiguous()
+    grouped_gemm_fp8(a, scale_a, b, _f32_or_none(scale_b).contiguous(), seg[: batch_size + 1],
+                     weight_indices, c, epilogue=0)
+    return c

@@ -1,0 +1,187 @@
+"""The oracle (oracle/restate.py) against vectors produced by running the
+reference itself (tests/golden/make_golden.py).  CPU only."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import restate as R
+
+
+def t(a, dtype=None):
+    x = torch.from_numpy(np.ascontiguousarray(a))
+    return x if dtype is None else x.to(dtype)
+
+
+@pytest.mark.parametrize("case", ["gate_small", "gate_v3", "gate_flat"])
+def test_gate_matches_reference(golden, case):
+    c = golden.case(case)
+    k, ng, tg = (int(v) for v in c["params"])
+    x = t(c["x"], torch.bfloat16)
+    kw = dict(top_k=k, n_group=ng, topk_group=tg, scoring_func="sigmoid")
+    assert R.gate_margin_fp64(x, t(c["W"]), t(c["bias"]), **kw) > 1e-5
+    idx, w = R.gate_forward(x, t(c["W"]), t(c["bias"]), norm_topk_prob=True,
+                            routed_scaling_factor=float(c["scale"]), **kw)
+    ri, rw = R.canonical_rows(t(c["topk_idx"]), t(c["topk_weight"]))
+    oi, ow = R.canonical_rows(idx, w)
+    assert torch.equal(oi, ri)
+    torch.testing.assert_close(ow, rw, rtol=1e-6, atol=1e-7)
+
+
+def test_moe_dense_matches_reference(golden):
+    c = golden.case("moe_dense")
+    x = t(c["x"])
+    idx, w = R.gate_forward(x, t(c["gate_W"]), None, top_k=2, n_group=1, topk_group=1,
+                            scoring_func="sigmoid", routed_scaling_factor=1.0)
+    ri, rw = R.canonical_rows(t(c["topk_idx"]), t(c["topk_weight"]))
+    oi, ow = R.canonical_rows(idx, w)
+    assert torch.equal(oi, ri)
+    y = R.moe_infer_dense(x, t(c["topk_idx"]), t(c["topk_weight"]),
+                          t(c["gate_w"]), t(c["up_w"]), t(c["down_w"]))
+    torch.testing.assert_close(y, t(c["y"]), rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("case", ["prep_small", "prep_skew", "prep_empty_experts"])
+def test_preprocess_bit_exact(golden, case):
+    c = golden.case(case)
+    r, s2d, seg = R.run_moe_ep_preproess(t(c["topk_ids"]), int(c["num_experts"]))
+    assert r.dtype == torch.int64 and s2d.dtype == torch.int32 and seg.dtype == torch.int64
+    assert torch.equal(r, t(c["reorder_topk_ids"]))
+    assert torch.equal(s2d, t(c["src2dst"]))
+    assert torch.equal(seg, t(c["seg_indptr"]))
+    assert torch.equal(R.tokens_per_expert(t(c["topk_ids"]), int(c["num_experts"])),
+                       seg[1:] - seg[:-1])
+
+
+@pytest.mark.parametrize("name", ["all", "part"])
+def test_reorder_kernels(golden, name):
+    c = golden.case(f"reorder_{name}")
+    lo, hi = (int(v) for v in c["lohi"])
+    ids, s2d = t(c["topk_ids"]), t(c["src2dst"])
+    x = t(c["x"], torch.float16)
+    pre = R.pre_reorder(x, s2d, ids, None, lo, hi, torch.zeros(ids.numel(), x.shape[1], dtype=torch.float16))
+    assert torch.equal(pre, t(c["pre"], torch.float16))
+    gu = t(c["gateup"], torch.float16)
+    rids = t(c["reorder_topk_ids"])
+    z = lambda: torch.zeros(gu.shape[0], gu.shape[1] // 2, dtype=torch.float16)
+    torch.testing.assert_close(R.silu_and_mul(gu, rids, None, lo, hi, z()), t(c["silu"], torch.float16),
+                               rtol=2e-3, atol=1e-4)
+    torch.testing.assert_close(R.gelu_and_mul(gu, rids, None, lo, hi, z()), t(c["gelu"], torch.float16),
+                               rtol=2e-3, atol=1e-4)
+    post = R.post_reorder(t(c["down"], torch.float16), s2d, ids, t(c["topk_weights"]), lo, hi)
+    torch.testing.assert_close(post, t(c["post"], torch.float16), rtol=2e-3, atol=2e-3)
+    # tokens without a local expert are zero-filled by the reference
+    local = ((ids >= lo) & (ids <= hi)).any(dim=1)
+    assert torch.all(post[~local] == 0)
+
+
+def test_grouped_gemm_fp16(golden):
+    c = golden.case("ggemm_fp16")
+    out = R.grouped_gemm_plain(t(c["a"], torch.float16), t(c["b"], torch.float16),
+                               t(c["seg_indptr"]), t(c["weight_indices"]))
+    torch.testing.assert_close(out, t(c["c_triton"], torch.float16), rtol=2e-3, atol=2e-3)
+    torch.testing.assert_close(out, t(c["c_torch"], torch.float16), rtol=2e-3, atol=2e-3)
+
+
+def test_fp8_act_quant_scales_and_payload(golden):
+    c = golden.case("fp8_act")
+    x = t(c["x"], torch.bfloat16)
+    y, s = R.act_quant_fp8(x)
+    ref_s = t(c["s"])
+    assert torch.equal(s, ref_s), "scales must be bit-exact (amax/448 in fp32)"
+    assert s[1, 1] == 0 and torch.isnan(y.float()[1, 128:256]).all()
+    # The payload pin is torch's round-to-nearest-even e4m3 cast of x/s: the Triton
+    # interpreter's own fp8 cast is not RNE, so the reference payload bytes produced on
+    # CPU are not a usable golden.  Check the defining property instead: dequantised
+    # values are within half an e4m3 ulp of x/s.
+    g = x.float().reshape(-1, 128)
+    q = y.float().reshape(-1, 128)
+    ok = s.reshape(-1) > 0
+    ratio = (g[ok] / s.reshape(-1)[ok].unsqueeze(-1))
+    ulp = torch.maximum(torch.full_like(ratio, 2.0 ** -9),
+                        2.0 ** (torch.floor(torch.log2(ratio.abs().clamp_min(2.0 ** -6))) - 3))
+    assert torch.all((q[ok] - ratio).abs() <= ulp / 2 + 1e-7)
+
+
+def test_fp8_gemm_and_dequant(golden):
+    c = golden.case("fp8_gemm")
+    a = t(c["a"]).view(torch.float8_e4m3fn)
+    b = t(c["b"]).view(torch.float8_e4m3fn)
+    out = R.fp8_gemm(a, t(c["a_s"]), b, t(c["b_s"]), out_dtype=torch.float32)
+    assert R.rel_fro(out, t(c["c"])) < 1e-6
+    assert torch.equal(R.weight_dequant_fp8(b, t(c["b_s"])), t(c["b_dequant"]))
+
+
+def test_weight_quant_fp8_roundtrip():
+    g = torch.Generator().manual_seed(5)
+    w = torch.randn(200, 300, generator=g) * 0.02
+    q, s = R.weight_quant_fp8(w)
+    assert q.shape == w.shape and s.shape == (2, 3) and s.dtype == torch.float32
+    assert R.rel_fro(R.weight_dequant_fp8(q, s), w) < 0.04
+    assert float(q.float().abs().max()) == 448.0
+
+
+@pytest.mark.parametrize("nbits,width", [(4, 32), (4, 8), (2, 16), (8, 32), (1, 8)])
+def test_bitpack(golden, nbits, width):
+    c = golden.case(f"bitpack_{nbits}_{width}")
+    W = t(c["W"])
+    pr, e = R.pack_weights_over_rows(W, nbits, width)
+    pc, _ = R.pack_weights_over_cols(W, nbits, width)
+    assert e == int(c["e"])
+    assert pr.dtype == t(c["rows"]).dtype and torch.equal(pr, t(c["rows"]))
+    assert torch.equal(pc, t(c["cols"]))
+    assert torch.equal(R.unpack_over_rows(pr, nbits, W.shape[0]), W)
+    assert torch.equal(R.unpack_over_cols(pc, nbits, W.shape[1]), W)
+
+
+def test_w4a8_two_level(golden):
+    c = golden.case("w4a8")
+    packed, s, s4, z4 = R.w4a8_weight_quant(t(c["w"]))
+    assert torch.equal(packed, t(c["packed"]))
+    assert torch.equal(s, t(c["s"], torch.float16))
+    assert torch.equal(s4, t(c["s4"])) and torch.equal(z4, t(c["z4"]))
+    assert torch.equal(R.w4a8_weight_dequant(packed, s, s4, z4), t(c["dequant"], torch.float16))
+    a8, a8s = R.act_quant_int8(t(c["x"]), rounding="floor_half")
+    assert torch.equal(a8, t(c["a8"])) and torch.equal(a8s, t(c["a8s"], torch.float16))
+    out = R.w4a8_gemm(a8, a8s, packed, s, s4, z4, out_dtype=torch.float32)
+    assert R.rel_fro(out, t(c["c"])) < 1e-6
+
+
+@pytest.mark.parametrize("gs", [128, -1])
+def test_marlin_pack(golden, gs):
+    c = golden.case(f"marlin_g{gs}")
+    w = t(c["w"], torch.float16)
+    ref, q, sc = R.w4a16_fake_quantize_sym(w, gs)
+    assert torch.equal(q, t(c["q"]))
+    assert torch.equal(sc, t(c["scale"], torch.float16))
+    assert torch.equal(ref, t(c["ref"], torch.float16))
+    pk, psc = R.marlin_pack(q, sc, gs)
+    assert torch.equal(pk, t(c["packed"]))
+    assert torch.equal(psc, t(c["packed_scale"], torch.float16))
+
+
+def test_asym_int4_roundtrip():
+    g = torch.Generator().manual_seed(9)
+    w = torch.randn(64, 256, generator=g) * 0.02
+    q, sc, z = R.w4a16_quantize_asym(w)
+    assert q.max() <= 15 and sc.dtype == torch.bfloat16 and z.dtype == torch.bfloat16
+    assert R.rel_fro(R.w4a16_dequant(q, sc, z, dtype=torch.float32), w) < 0.12
+
+
+def test_layer_fp8_independent_of_ep_and_close_to_dense():
+    g = torch.Generator().manual_seed(0)
+    T, H, I, E, k = 64, 256, 128, 8, 2
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    Wg = torch.randn(E, H, generator=g) * 0.02
+    idx, w = R.gate_forward(x, Wg, None, top_k=k, scoring_func="softmax")
+    gw = torch.randn(E, I, H, generator=g) * 0.02
+    uw = torch.randn(E, I, H, generator=g) * 0.02
+    dw = torch.randn(E, H, I, generator=g) * 0.02
+    q13 = [R.weight_quant_fp8(torch.cat([gw[e], uw[e]], 0)) for e in range(E)]
+    q2 = [R.weight_quant_fp8(dw[e]) for e in range(E)]
+    w13 = torch.stack([a for a, _ in q13]); w13s = torch.stack([b for _, b in q13])
+    w2 = torch.stack([a for a, _ in q2]); w2s = torch.stack([b for _, b in q2])
+    y1 = R.moe_layer_fp8(x, idx, w, w13, w13s, w2, w2s, ep_size=1)
+    y4 = R.moe_layer_fp8(x, idx, w, w13, w13s, w2, w2s, ep_size=4)
+    assert torch.equal(y1, y4)
+    dense = R.moe_infer_dense(x.float(), idx, w, gw, uw, dw)
+    assert R.rel_fro(y1, dense) < 0.1   # fp8 weight+activation quantisation noise
