@@ -1,0 +1,371 @@
+"""Benchmark of the expert-parallel quantized MoE layer.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one forward pass of the layer over one batch of synthetic tokens per rank
+(configs[3] of the benchmark spec: DeepSeek-V3 shape, 256 experts, top-8, hidden 7168,
+SwiGLU 2048, e4m3 weights with 128x128 scales, 4096 tokens per rank, Zipf-skewed expert
+popularity; EP = N).  For N > 1 launch with torch.distributed.run, one rank per GPU.
+Rank 0 prints ONE JSON line.
+
+`value` is whole-job tokens/s with the tokens already resident in HBM, timed with CUDA
+events on the launching stream (max over ranks).  `e2e` is the same metric through the
+public layer call with HOST buffers: the pinned host->device copy of the step's tokens and
+the device->host read of its output are inside the timed region.  `roofline` describes the
+dominant kernel (the gate/up grouped GEMM), `cpu_baseline` times the CPU restatement of the
+reference's torch path on the host cores on a bounded sample.
+
+--impl reference times that CPU path alone (the reference is Python + Triton and has no
+installable CPU build; its torch code path is what oracle/restate.py restates).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "ep_moe_layer_tokens_per_s"
+UNIT = "tokens/s"
+NOMINAL_FP8_TFLOPS = 4500.0
+NOMINAL_HBM_GBS = 8000.0
+
+
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_id):
+        self.index, self.proc, self.lines = gpu_id, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], None, set()
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx = float(f[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def _dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+# ------------------------------------------------------------------------------------------
+# CPU baseline: the reference's torch path (MoEGate + moe_infer per-expert loop,
+# moe/all2all_moe.py:60-118, 186-280) as restated in oracle/restate.py, on the host cores.
+# ------------------------------------------------------------------------------------------
+def cpu_reference_run(shape, layer_weights_fn, sample_tokens, steps, warmup, budget_s=None):
+    """Times gate + per-expert loop on `sample_tokens` tokens; returns (tokens/s, cores, tokens used).
+    With budget_s the sample is resized after a probe step so that all steps fit the budget."""
+    from oracle import restate as R
+    from llm_kernels_b200 import workloads as WL
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = torch.get_num_threads()
+    W, bias = WL.router_params(shape)
+    gw, uw, dw = layer_weights_fn()           # bf16 CPU tensors [E,I,H], [E,I,H], [E,H,I]
+
+    def one(x):
+        t0 = time.perf_counter()
+        idx, w = R.gate_forward(x, W, bias, top_k=shape.top_k, n_group=shape.n_group,
+                                topk_group=shape.topk_group, scoring_func=shape.scoring,
+                                routed_scaling_factor=shape.scaling)
+        R.moe_infer_dense(x, idx, w, gw, uw, dw)
+        return time.perf_counter() - t0
+
+    if budget_s is not None:
+        probe = one(WL.tokens(shape, rank=0, n=64))
+        per_step = budget_s / max(steps + warmup, 1)
+        # cost is roughly affine in tokens (weights stream once per step); scale conservatively
+        sample_tokens = int(max(64, min(shape.tokens, 64 * per_step / max(probe, 1e-3))))
+        sample_tokens -= sample_tokens % 64
+    x = WL.tokens(shape, rank=0, n=sample_tokens)
+    times = [one(x) for _ in range(warmup + steps)][warmup:]
+    return sample_tokens / statistics.median(times), cores, sample_tokens
+
+
+def cpu_weights_from_layer(layer, shape):
+    """Dequantized bf16 copies of the layer's own quantized experts, moved to the host."""
+    from oracle import restate as R
+    E, I, H = shape.experts, shape.inter, shape.hidden
+    gw = torch.empty(E, I, H, dtype=torch.bfloat16)
+    uw = torch.empty(E, I, H, dtype=torch.bfloat16)
+    dw = torch.empty(E, H, I, dtype=torch.bfloat16)
+    for e in range(E):
+        w13 = R.weight_dequant_fp8(layer.w13_weight[e], layer.w13_weight_scale[e], dtype=torch.bfloat16)
+        gw[e].copy_(w13[:I]); uw[e].copy_(w13[I:])
+        dw[e].copy_(R.weight_dequant_fp8(layer.w2_weight[e], layer.w2_weight_scale[e], dtype=torch.bfloat16))
+    return gw, uw, dw
+
+
+def cpu_weights_random(shape):
+    """Host bf16 expert weights ~N(0, 0.02): one drawn matrix per projection, rescaled per expert
+    (drawing 11 G normal variates on the host would take longer than the measurement)."""
+    E, I, H = shape.experts, shape.inter, shape.hidden
+    g = torch.Generator().manual_seed(shape.seed)
+    base_g = torch.randn(I, H, generator=g) * 0.02
+    base_u = torch.randn(I, H, generator=g) * 0.02
+    base_d = torch.randn(H, I, generator=g) * 0.02
+    gw = torch.empty(E, I, H, dtype=torch.bfloat16); uw = torch.empty_like(gw)
+    dw = torch.empty(E, H, I, dtype=torch.bfloat16)
+    for e in range(E):
+        f = 1.0 + 0.001 * e
+        gw[e] = (base_g * f).to(torch.bfloat16); uw[e] = (base_u * f).to(torch.bfloat16)
+        dw[e] = (base_d * f).to(torch.bfloat16)
+    return gw, uw, dw
+
+
+def run_reference(args):
+    rank, world, _ = _dist_env()
+    if rank != 0:
+        return
+    from llm_kernels_b200 import workloads as WL
+    shape = WL.CONFIG3
+    t0 = time.perf_counter()
+    v, cores, sample = cpu_reference_run(shape, lambda: cpu_weights_random(shape), args.cpu_tokens, args.steps,
+                                         args.warmup, budget_s=150.0)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sample / v,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "config": _config(shape, args.gpus),
+        "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{sample} of {shape.tokens} tokens per step, all {shape.experts} experts, bf16 "
+                                   f"weights, torch CPU per-expert loop ({time.perf_counter() - t0:.0f} s incl. setup)"},
+        "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def _config(shape, n):
+    return {"workload": f"configs[3]: DeepSeek-V3-shape fp8 blockwise MoE layer, EP={n}, {shape.tokens} tokens/rank, "
+                        f"{shape.experts} experts top-{shape.top_k} (groups {shape.n_group}/{shape.topk_group}), hidden "
+                        f"{shape.hidden}, SwiGLU {shape.inter}, Zipf(1.1)-biased routing, seed {shape.seed}",
+            "tokens_per_rank": shape.tokens, "ep_size": n,
+            "l2": "inputs larger than L2: each step streams the rank's expert weights "
+                  f"({shape.experts // n * 3 * shape.hidden * shape.inter / 1e9:.2f} GB) and 4 rotating token batches"}
+
+
+# ------------------------------------------------------------------------------------------
+def measure_fp8_peak(dev):
+    """Dense e4m3 GEMM 8192^3 through torch._scaled_mm (cuBLASLt), best of 10, TFLOP/s."""
+    try:
+        n = 8192
+        a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+        b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+        one = torch.ones((), device=dev)
+        best = None
+        for _ in range(12):
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            e.record(); e.synchronize()
+            ms = s.elapsed_time(e)
+            best = ms if best is None else min(best, ms)
+        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+    except Exception:
+        return None
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    from llm_kernels_b200 import workloads as WL
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+
+    rank, world, local = _dist_env()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    shape = WL.CONFIG3
+    T, H, k = shape.tokens, shape.hidden, shape.top_k
+
+    layer = DeepseekV3MoE(WL.make_config(shape, ep_size=world), device=dev).eval()
+    WL.fill_layer_gpu(layer, shape)
+    nbatch = 4
+    xs = [WL.tokens(shape, rank=rank * 16 + i, device=dev).view(1, T, H) for i in range(nbatch)]
+    host_in = [x.cpu().pin_memory() for x in xs]
+    host_out = torch.empty(T, H, dtype=torch.bfloat16).pin_memory()
+    dev_in = torch.empty(1, T, H, dtype=torch.bfloat16, device=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, steps):
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for i in range(steps):
+            fn(i)
+        e.record()
+        barrier()
+        ms = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    step = lambda i: layer(xs[i % nbatch])
+
+    def step_e2e(i):
+        dev_in.copy_(host_in[i % nbatch], non_blocking=True)
+        y = layer(dev_in)
+        host_out.copy_(y.view(T, H), non_blocking=True)
+        torch.cuda.current_stream().synchronize()     # the caller holds the result
+
+    for i in range(args.warmup):
+        step(i)
+    layer.check_status()
+    sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid))
+    sampler.start()
+    time.sleep(0.3)
+    ms = timed(step, args.steps)
+    clocks = sampler.stop()
+    layer.check_status()
+    for i in range(min(args.warmup, 3)):
+        step_e2e(i)
+    ms_e2e = timed(step_e2e, args.steps)
+
+    # per-stage device times (separate pass, events between the stages)
+    layer.stage_events = []
+    barrier()
+    for i in range(args.steps):
+        step(i)
+    torch.cuda.synchronize()
+    ev = layer.stage_events
+    layer.stage_events = None
+    stages = {}
+    for (n0, e0), (n1, e1) in zip(ev[:-1], ev[1:]):
+        if n1 != "start":
+            stages[n1] = stages.get(n1, 0.0) + e0.elapsed_time(e1)
+    stages = {n: v / args.steps for n, v in stages.items()}
+    rows = layer.last_recv_rows
+
+    if rank == 0:
+        peaks = _peaks()
+        tokens_per_s = world * T * args.steps / (ms * 1e-3)
+        e2e_tokens_per_s = world * T * args.steps / (ms_e2e * 1e-3)
+        El, I = shape.experts // world, shape.inter
+        # dominant kernel: gate/up grouped GEMM.  Algorithmic bytes per launch: every local expert's
+        # w13 (e4m3) + its f32 block scales once, the activation rows (packed e4m3 + f32 scales) once,
+        # the e4m3 SwiGLU output + scales once.
+        g1_bytes = (El * (2 * I * H + (2 * I // 128) * (H // 128) * 4) + rows * (H + H // 32) + rows * (I + I // 32))
+        g1_flops = 4.0 * H * I * rows
+        g2_flops = 2.0 * H * I * rows
+        g1_s = stages.get("gemm1_swiglu", float("nan")) * 1e-3
+        g2_s = stages.get("gemm2", float("nan")) * 1e-3
+        hbm_bound = world == 1
+        fp8_peak = measure_fp8_peak(dev) if args.fp8_peak else None
+        tensor_peak = fp8_peak or 2 * peaks["bf16_tflops"]
+        if hbm_bound:
+            ach = g1_bytes / g1_s / 1e9
+            roof = {"kernel": "gemm_fp8_block_kernel (gate/up + SwiGLU epilogue)", "bound": "hbm", "achieved": ach,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                    "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": g1_bytes}
+        else:
+            ach = g1_flops / g1_s / 1e12
+            roof = {"kernel": "gemm_fp8_block_kernel (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": ach,
+                    "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak, "traffic": None,
+                    "peak_source": "torch._scaled_mm e4m3 8192^3 measured in this run" if fp8_peak else
+                                   f"2 x {peaks['source']} bf16 cuBLAS", "algorithmic_flops": g1_flops}
+        line = {
+            "metric": METRIC, "value": tokens_per_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": _config(shape, world),
+            "clocks": clocks,
+            "e2e": {"value": e2e_tokens_per_s, "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
+                    "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e / args.steps},
+            "gpu_launches": 8 * args.steps,
+            "roofline": roof,
+            "tokens_per_s_per_gpu": tokens_per_s / world,
+            "stages_ms": stages, "rows_rank0": rows,
+            "grouped_gemm": {"gemm1_tflops": g1_flops / g1_s / 1e12, "gemm2_tflops": g2_flops / g2_s / 1e12,
+                             "both_tflops": (g1_flops + g2_flops) / (g1_s + g2_s) / 1e12,
+                             "frac_of_nominal_fp8_4500": (g1_flops + g2_flops) / (g1_s + g2_s) / 1e12 / NOMINAL_FP8_TFLOPS,
+                             "fp8_peak_measured_tflops": fp8_peak},
+        }
+        if world == 1 and args.cpu_tokens > 0:
+            t0 = time.perf_counter()
+            v, cores, _ = cpu_reference_run(shape, lambda: cpu_weights_from_layer(layer, shape), args.cpu_tokens, 2, 1)
+            line["cpu_baseline"] = {
+                "value": v, "unit": UNIT, "cores": cores, "kind": "port",
+                "sample": f"{args.cpu_tokens} of {T} tokens, all {shape.experts} experts (dequantized bf16 copies of the "
+                          f"same weights), torch CPU per-expert loop, median of 2 after 1 warm-up "
+                          f"({time.perf_counter() - t0:.0f} s incl. setup)"}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens in the CPU baseline sample (0 = skip)")
+    ap.add_argument("--no-fp8-peak", dest="fp8_peak", action="store_false")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

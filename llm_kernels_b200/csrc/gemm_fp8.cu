@@ -255,7 +255,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
       for (int kb = 0; kb < KB; ++kb) {
         const float s0 = sa_n * b0_n, s1 = sa_n * b1_n;
         if (kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
-        if (!ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag)) { ok = false; break; }
+        // warp-uniform outcome: the TMEM loads below need the whole warp converged
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t tcol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
 #pragma unroll
@@ -309,7 +310,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
         sh->amax[buf][hsel][r_in_tile] = amax;
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&sh->amax_bar[buf]);
-        if (!ptx::mbar_wait(&sh->amax_bar[buf], (it >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&sh->amax_bar[buf], (it >> 1) & 1u, abort_flag))) { ok = false; break; }
         amax = fmaxf(amax, sh->amax[buf][hsel ^ 1][r_in_tile]);
         if (row_ok) {
           const float scale = __fdiv_rn(amax, 448.f);

@@ -118,6 +118,15 @@ class DeepseekV3MoE(nn.Module):
         self._buffers_cache = {}
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         self.last_recv_rows = None
+        # Optional per-stage timing: set to a list and every forward appends
+        # (stage name, CUDA event recorded when the stage's launches were queued).
+        self.stage_events = None
+
+    def _mark(self, name):
+        if self.stage_events is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.stage_events.append((name, ev))
 
     # ---- weights ---------------------------------------------------------------------
     @torch.no_grad()
@@ -147,7 +156,9 @@ class DeepseekV3MoE(nn.Module):
     @torch.no_grad()
     def forward(self, hidden_states):
         orig_shape = hidden_states.shape
+        self._mark("start")
         topk_idx, topk_weight = self.gate(hidden_states)
+        self._mark("router")
         x = hidden_states.reshape(-1, orig_shape[-1])
         if not x.is_contiguous():
             x = x.contiguous()
@@ -169,12 +180,14 @@ class DeepseekV3MoE(nn.Module):
         S = T * k
         assert x.dtype == torch.bfloat16, "activations must be bfloat16"
         reorder_ids, src2dst, seg_indptr = G.run_moe_ep_preproess(topk_ids, E)
+        self._mark("route_metadata")
         # packed record: e4m3 row + f32 scales, padded so rows stay 16-byte aligned for TMA
         rec = (H + (H // 128) * 4 + 15) // 16 * 16
         send = self._buf("send", (S, rec), torch.uint8)
         send_q = send[:, :H]
         send_s = send[:, H:H + (H // 128) * 4].view(torch.float32)
         G.permute_quant_fp8(x, src2dst, topk_ids, 0, E - 1, send_q, send_s)
+        self._mark("permute_quant")
 
         if self.ep_size == 1:
             a_q, a_s, rows = send_q, send_s, S
@@ -189,6 +202,7 @@ class DeepseekV3MoE(nn.Module):
             ep_comm.dispatch(plan, send, recv)
             a_q, a_s = recv[:, :H], recv[:, H:H + (H // 128) * 4].view(torch.float32)
             seg, widx = plan.seg_indptr, plan.weight_indices
+            self._mark("dispatch_a2a")
         self.last_recv_rows = rows
 
         h_q = self._buf("h_q", (rows, I), torch.uint8)
@@ -197,15 +211,19 @@ class DeepseekV3MoE(nn.Module):
         if rows > 0:
             G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx,
                                h_q, h_s, epilogue=1, status_word=self._status)
+            self._mark("gemm1_swiglu")
             G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
                                down, None, epilogue=0, status_word=self._status)
+            self._mark("gemm2")
 
         if self.ep_size > 1:
             back = self._buf("back", (S, H), torch.bfloat16)
             down = ep_comm.combine(plan, down, back)
+            self._mark("combine_a2a")
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
         G.post_reorder_triton_kernel[(T,)](down, out, src2dst, topk_ids, topk_weight, 0, E - 1, k, H,
                                            BLOCK_SIZE=512)
+        self._mark("post_reorder")
         return out
 
     def check_status(self):

@@ -25,6 +25,13 @@ FP8_MAX = 448.0
 FP8 = torch.float8_e4m3fn
 
 
+def _div_const(t: torch.Tensor, c: float) -> torch.Tensor:
+    """t / c as a true IEEE division on every device.  (torch's CUDA kernels turn a
+    division by a Python scalar into a multiplication by its reciprocal, which is
+    off by one ulp about half the time; tensor / tensor divides.)"""
+    return t / torch.full_like(t, c)
+
+
 # --------------------------------------------------------------------------
 # Router  (moe/all2all_moe.py:60-118)
 # --------------------------------------------------------------------------
@@ -55,20 +62,19 @@ def gate_select(scores: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
                 n_group: int, topk_group: int):
     """Group-limited top-k of moe/all2all_moe.py:75-106 on given scores.
 
-    Returns (topk_idx [T,k] in descending choice-score order, margin) where
-    margin is the smallest gap that decided any selection in any row (group
-    cut and expert cut)."""
+    Returns (topk_idx [T,k] in descending choice-score order, margin [T]) where
+    margin is, per token, the smallest gap that decided a selection (group cut
+    and expert cut)."""
     T, E = scores.shape
     sfc = scores if bias is None else scores + bias.unsqueeze(0).to(scores.dtype)
-    margin = torch.full((), float("inf"), dtype=scores.dtype, device=scores.device)
+    margin = torch.full((T,), float("inf"), dtype=scores.dtype, device=scores.device)
     if n_group > 1:
         grouped = sfc.view(T, n_group, E // n_group)
         group_scores = grouped.topk(2, dim=-1)[0].sum(dim=-1)          # :80-82
         gsorted = torch.sort(group_scores, dim=-1, descending=True, stable=True)
         group_idx = gsorted[1][:, :topk_group]                         # :84-85
         if topk_group < n_group:
-            margin = torch.minimum(
-                margin, (gsorted[0][:, topk_group - 1] - gsorted[0][:, topk_group]).min())
+            margin = torch.minimum(margin, gsorted[0][:, topk_group - 1] - gsorted[0][:, topk_group])
         group_mask = torch.zeros_like(group_scores)
         group_mask.scatter_(1, group_idx, 1)                           # :88-89
         score_mask = group_mask.unsqueeze(-1).expand(T, n_group, E // n_group).reshape(T, E)
@@ -78,7 +84,7 @@ def gate_select(scores: torch.Tensor, bias: Optional[torch.Tensor], top_k: int,
     ssorted = torch.sort(tmp, dim=-1, descending=True, stable=True)
     topk_idx = ssorted[1][:, :top_k]                                   # :104-106
     if top_k < E:
-        margin = torch.minimum(margin, (ssorted[0][:, top_k - 1] - ssorted[0][:, top_k]).min())
+        margin = torch.minimum(margin, ssorted[0][:, top_k - 1] - ssorted[0][:, top_k])
     return topk_idx, margin
 
 
@@ -100,15 +106,20 @@ def gate_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     return topk_idx, topk_weight
 
 
-def gate_margin_fp64(x, weight, bias, *, top_k, n_group=1, topk_group=1,
-                     scoring_func="sigmoid") -> float:
-    """Smallest selection gap when the router is evaluated in fp64.  A seeded
-    input is admissible for bit-exact routing tests only if this is well above
-    fp32 summation noise (the tests require > 1e-5)."""
+def gate_margins_fp64(x, weight, bias, *, top_k, n_group=1, topk_group=1,
+                      scoring_func="sigmoid") -> torch.Tensor:
+    """Per-token smallest selection gap when the router is evaluated in fp64.  A
+    token is admissible for bit-exact routing comparison only if its gap is well
+    above f32 summation noise: two correct f32 routers may legitimately differ on
+    a token whose k-th and (k+1)-th scores are closer than that."""
     scores = gate_scores(x, weight, scoring_func, dtype=torch.float64)
     b = None if bias is None else bias.double()
     _, margin = gate_select(scores, b, top_k, n_group, topk_group)
-    return float(margin)
+    return margin
+
+
+def gate_margin_fp64(x, weight, bias, **kw) -> float:
+    return float(gate_margins_fp64(x, weight, bias, **kw).min())
 
 
 def canonical_rows(topk_idx: torch.Tensor, topk_weight: torch.Tensor):
@@ -155,7 +166,7 @@ def act_quant_fp8(x: torch.Tensor, block_size: int = 128):
     amax == 0 gives s == 0 and y == NaN exactly as the reference does."""
     assert x.is_contiguous() and x.shape[-1] % block_size == 0
     g = x.float().reshape(-1, block_size)
-    s = g.abs().amax(dim=-1) / FP8_MAX
+    s = _div_const(g.abs().amax(dim=-1), FP8_MAX)
     y = (g / s.unsqueeze(-1)).to(FP8)
     return (y.reshape(x.shape),
             s.reshape(*x.shape[:-1], x.shape[-1] // block_size))
@@ -174,7 +185,7 @@ def weight_quant_fp8(w: torch.Tensor, block_size: int = 128):
     scale shape [ceil(M/bs), ceil(N/bs)]); the reference ships no fp8 weight
     quantizer."""
     blk, M, N = _blocks(w.float(), block_size)
-    s = blk.abs().amax(dim=(-1, -2)) / FP8_MAX
+    s = _div_const(blk.abs().amax(dim=(-1, -2)), FP8_MAX)
     y = blk / s[..., None, None]
     y = y.permute(0, 2, 1, 3).reshape(blk.shape[0] * block_size, blk.shape[1] * block_size)
     return y[:M, :N].contiguous().to(FP8), s
@@ -245,7 +256,7 @@ def act_quant_int8(x: torch.Tensor, block_size: int = 128, rounding: str = "half
     or quantization/w4a8_kernel.py:159-168 (rounding='floor_half',
     floor(x/s + 0.5)).  s = amax/127 (fp32), stored as fp16."""
     g = x.float().reshape(-1, block_size)
-    s = g.abs().amax(dim=-1) / 127.0
+    s = _div_const(g.abs().amax(dim=-1), 127.0)
     q = g / s.unsqueeze(-1)
     if rounding == "half_away":
         q = torch.sign(q) * torch.floor(q.abs() + 0.5)
@@ -486,12 +497,12 @@ def w4a8_weight_quant(x: torch.Tensor, block_size: int = 128, group: int = 128):
     z4 int8 [M,N/128])."""
     M, N = x.shape
     blk, _, _ = _blocks(x.float(), block_size)
-    s = blk.abs().amax(dim=(-1, -2)) / 119.0
+    s = _div_const(blk.abs().amax(dim=(-1, -2)), 119.0)
     y8 = torch.clamp(torch.floor(blk / s[..., None, None] + 0.5), -119.0, 119.0)
     y8 = y8.permute(0, 2, 1, 3).reshape(blk.shape[0] * block_size, -1)[:M, :N]
     g = y8.reshape(M, N // group, group)
     mx, mn = g.amax(-1), g.amin(-1)
-    s4 = torch.floor((mx - mn) / 15.0 + 0.5)
+    s4 = torch.floor(_div_const(mx - mn, 15.0) + 0.5)
     z4 = torch.floor(-mn / s4 + 0.5)
     q = torch.clamp(torch.floor(g / s4.unsqueeze(-1) + 0.5) + z4.unsqueeze(-1), 0, 15)
     q = q.reshape(M, N).to(torch.uint8)
