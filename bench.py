@@ -171,7 +171,7 @@ def run_reference(args):
     if rank != 0:
         return
     from llm_kernels_b200 import workloads as WL
-    shape = WL.CONFIG3
+    shape = WL.CONFIG3 if args.shape == "cfg3" else WL.CONFIG3_SMALL
     t0 = time.perf_counter()
     v, cores, sample = cpu_reference_run(shape, lambda: cpu_weights_random(shape), args.cpu_tokens, args.steps,
                                          args.warmup, budget_s=150.0)
@@ -189,7 +189,7 @@ def run_reference(args):
 
 
 def _config(shape, n):
-    return {"workload": f"configs[3]: DeepSeek-V3-shape fp8 blockwise MoE layer, EP={n}, {shape.tokens} tokens/rank, "
+    return {"workload": f"{'configs[3]' if shape.experts == 256 else 'configs[3] cut to 1/8 (profiling case)'}: DeepSeek-V3-shape fp8 blockwise MoE layer, EP={n}, {shape.tokens} tokens/rank, "
                         f"{shape.experts} experts top-{shape.top_k} (groups {shape.n_group}/{shape.topk_group}), hidden "
                         f"{shape.hidden}, SwiGLU {shape.inter}, Zipf(1.1)-biased routing, seed {shape.seed}",
             "tokens_per_rank": shape.tokens, "ep_size": n,
@@ -229,7 +229,7 @@ def run_ours(args):
     dev = torch.device("cuda", local)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    shape = WL.CONFIG3
+    shape = WL.CONFIG3 if args.shape == "cfg3" else WL.CONFIG3_SMALL
     T, H, k = shape.tokens, shape.hidden, shape.top_k
 
     layer = DeepseekV3MoE(WL.make_config(shape, ep_size=world), device=dev).eval()
@@ -357,6 +357,8 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shape", default="cfg3", choices=["cfg3", "small"],
+                    help="cfg3 = the benchmark configuration; small = 1/8 of its experts and tokens (profiler captures)")
     ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens in the CPU baseline sample (0 = skip)")
     ap.add_argument("--no-fp8-peak", dest="fp8_peak", action="store_false")
     args = ap.parse_args()

@@ -60,7 +60,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([nvcc, "-shared", "-o", LIB, *objs, "-Xcompiler", "-fvisibility=hidden"])
+    subprocess.check_call([nvcc, "-arch=sm_100a", "-shared", "-o", LIB, *objs])
     return LIB
 
 

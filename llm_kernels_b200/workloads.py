@@ -38,6 +38,11 @@ CONFIG0 = LayerShape("cfg0_fp8_small", 512, 1024, 2048, 8, 2, 1, 1, "softmax", 1
 CONFIG3 = LayerShape("cfg3_dsv3_fp8", 4096, 7168, 2048, 256, 8, 8, 4, "sigmoid", 2.5, 3, zipf_bias=1.0)
 
 
+# configs[3] cut down for profiler captures and quick runs: same hidden/intermediate sizes (same
+# tiles and K loop), 1/8 of the experts and of the slots -> 1.4 GB of weights (still far above L2)
+CONFIG3_SMALL = LayerShape("cfg3_small", 1024, 7168, 2048, 32, 4, 4, 2, "sigmoid", 2.5, 3, zipf_bias=1.0)
+
+
 def make_config(shape: LayerShape, ep_size: int = 1) -> Config:
     c = Config()
     c.hidden_size, c.moe_intermediate_size = shape.hidden, shape.inter
