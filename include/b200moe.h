@@ -126,6 +126,24 @@ B200MOE_API int b200moe_route_metadata(const int64_t* topk_ids, int64_t num_slot
                            int64_t* reorder_topk_ids, int32_t* src2dst, int64_t* seg_indptr,
                            void* workspace, size_t workspace_bytes, void* stream);
 
+/* Same result as b200moe_route_metadata, for callers that cannot supply a workspace: code
+ * running inside a process whose framework took all device memory for its own pool, a plug-in
+ * that only ever sees its input and output buffers, or a loop that must never reach cudaMalloc
+ * because that call synchronises the device.  This entry point has no counterpart in the
+ * reference.  Its scratch is a 1 MiB array built into the library (resident on every GPU that
+ * loads the library, until the process exits), which bounds the problem size:
+ *     ceil(num_slots / 1024) * num_experts <= 262144
+ * (e.g. 1 M slots x 256 experts, or 262 k slots x 1024 experts); larger requests return
+ * B200MOE_BAD_SHAPE and launch nothing.  It performs no device allocation of any kind.
+ * The first call on each GPU looks up the array's device address (once, with that GPU
+ * current); make that first call outside any stream capture.  All calls on one GPU share the
+ * array: two calls whose kernels may overlap on the GPU (different streams without an
+ * ordering between them) race and give wrong results -- order them on one stream or with
+ * events.  Nothing needs zeroing between calls. */
+B200MOE_API int b200moe_route_metadata_noalloc(const int64_t* topk_ids, int64_t num_slots, int num_experts,
+                                   int64_t* reorder_topk_ids, int32_t* src2dst,
+                                   int64_t* seg_indptr, void* stream);
+
 /* pre_reorder_triton_kernel (moe/group_gemm_kernel.py:81-117): for every slot
  * whose expert is in [start_expert_id, end_expert_id] (inclusive) copy the
  * token's row to out[src2dst[slot]], multiplied by 1/a1_scales[e-start] when

@@ -11,6 +11,8 @@
 //                           + (same-expert slots earlier in this chunk)
 // No step depends on the order in which atomics land, so the result is the
 // stable sort bit for bit.  Ids outside [0, E) are ignored (src2dst = -1).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -148,4 +150,76 @@ extern "C" int b200moe_route_metadata(const int64_t* topk_ids, int64_t num_slots
   route_rank_kernel<<<grid, kWarpsPerBlock * 32, smem, st>>>(topk_ids, num_slots, num_experts, scratch,
                                                              seg_indptr, reorder_topk_ids, src2dst);
   return check_launch("route_metadata");
+}
+
+// ---- variant that needs no caller-provided scratch ------------------------------------------
+//
+// Some callers have no way to hand this library a scratch buffer: a serving process whose
+// framework reserved all of device memory for its own pool at start-up, a plug-in that is only
+// given its input and output tensors, or a latency-critical loop in which cudaMalloc (which
+// synchronises the whole device) must never run.  For them the counting sort's chunk-histogram
+// table lives in a fixed array inside the library image.  Every GPU that loads the library
+// carries this 1 MiB until the process exits, whether the entry point is used or not.
+namespace b200moe {
+
+constexpr int64_t kStaticScratchInts = 262144;  // 1 MiB: chunks (1024 slots each) x experts
+static __device__ __align__(256) int32_t g_route_scratch[kStaticScratchInts];
+
+constexpr int kMaxDevices = 64;
+static std::mutex g_scratch_mutex;
+static int32_t* g_scratch_ptr[kMaxDevices] = {};  // device address of g_route_scratch, per GPU
+
+// In host code `g_route_scratch` is only a handle for the runtime, not a device address; the
+// address on the current device has to be asked for.  Done once per device, on first use.
+static int static_scratch_for_current_device(int32_t** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(B200MOE_UNSUPPORTED_DEVICE, "route_metadata_noalloc: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(B200MOE_UNSUPPORTED_DEVICE, "route_metadata_noalloc: device ordinal %d not in [0,%d)", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_ptr[dev] == nullptr) {
+    int32_t* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_route_scratch);
+    if (e != cudaSuccess || ptr == nullptr)
+      return fail(B200MOE_LAUNCH_FAILED, "route_metadata_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    g_scratch_ptr[dev] = ptr;
+  }
+  *out = g_scratch_ptr[dev];
+  return B200MOE_OK;
+}
+
+}  // namespace b200moe
+
+extern "C" int b200moe_route_metadata_noalloc(const int64_t* topk_ids, int64_t num_slots,
+                                              int num_experts, int64_t* reorder_topk_ids,
+                                              int32_t* src2dst, int64_t* seg_indptr, void* stream) {
+  B200MOE_REQUIRE(seg_indptr, B200MOE_BAD_ARG, "route_metadata_noalloc: null seg_indptr");
+  B200MOE_REQUIRE(num_experts >= 1 && num_experts <= kMaxExperts, B200MOE_BAD_SHAPE,
+                  "route_metadata_noalloc: num_experts=%d not in [1,%d]", num_experts, kMaxExperts);
+  B200MOE_REQUIRE(num_slots >= 0 && num_slots < (int64_t(1) << 31), B200MOE_BAD_SHAPE,
+                  "route_metadata_noalloc: num_slots=%lld does not fit int32 rows", (long long)num_slots);
+  const int64_t chunks = (num_slots + kChunk - 1) / kChunk;
+  B200MOE_REQUIRE(chunks * num_experts <= kStaticScratchInts, B200MOE_BAD_SHAPE,
+                  "route_metadata_noalloc: ceil(num_slots/%d) * num_experts = %lld exceeds the built-in scratch of "
+                  "%lld entries; use b200moe_route_metadata with a caller-provided workspace",
+                  kChunk, (long long)(chunks * num_experts), (long long)kStaticScratchInts);
+  cudaStream_t st = as_stream(stream);
+  if (num_slots == 0) {
+    cudaMemsetAsync(seg_indptr, 0, sizeof(int64_t) * (num_experts + 1), st);
+    return check_launch("route_metadata_noalloc(memset)");
+  }
+  B200MOE_REQUIRE(topk_ids && reorder_topk_ids && src2dst, B200MOE_BAD_ARG, "route_metadata_noalloc: null pointer");
+  int32_t* scratch = nullptr;
+  if (int rc = static_scratch_for_current_device(&scratch)) return rc;
+  // The table keeps whatever the previous call left in it.  Nothing has to be cleared: the
+  // histogram pass stores (not adds) every one of the chunks x num_experts entries that the
+  // later passes read.
+  const unsigned grid = static_cast<unsigned>((chunks + kWarpsPerBlock - 1) / kWarpsPerBlock);
+  const size_t smem = sizeof(int32_t) * kWarpsPerBlock * num_experts;
+  route_hist_kernel<<<grid, kWarpsPerBlock * 32, smem, st>>>(topk_ids, num_slots, num_experts, scratch);
+  route_scan_kernel<<<1, 1024, 0, st>>>(scratch, chunks, num_experts, seg_indptr);
+  route_rank_kernel<<<grid, kWarpsPerBlock * 32, smem, st>>>(topk_ids, num_slots, num_experts, scratch,
+                                                             seg_indptr, reorder_topk_ids, src2dst);
+  return check_launch("route_metadata_noalloc");
 }
