@@ -36,6 +36,10 @@ METRIC = "ep_moe_layer_tokens_per_s"
 UNIT = "tokens/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE gate/up launch in the ncu capture summarised in
+# profiles/gemm_fp8_block_kernel_cfg3_small.md (32 experts, 4096 rows).  At EP = 1 the full workload has
+# 8x the experts and 8x the rows, and the traffic (weights once + rows once) grows in proportion.
+NCU_GEMM1_SMALL = {"dram_bytes": 991.911424e6 + 13.596928e6, "experts": 32, "rows": 4096}
 
 
 def _peaks():
@@ -313,7 +317,9 @@ def run_ours(args):
         if hbm_bound:
             ach = g1_bytes / g1_s / 1e9
             roof = {"kernel": "gemm_fp8_block_kernel (gate/up + SwiGLU epilogue)", "bound": "hbm", "achieved": ach,
-                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                    "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                    "traffic": NCU_GEMM1_SMALL["dram_bytes"] * El / NCU_GEMM1_SMALL["experts"]
+                    if rows == NCU_GEMM1_SMALL["rows"] * El // NCU_GEMM1_SMALL["experts"] else None,
                     "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": g1_bytes}
         else:
             ach = g1_flops / g1_s / 1e12
