@@ -10,14 +10,17 @@
 // TMEM stage, epilogue warps read it back (tcgen05.ld) and FMA it into register
 // accumulators while the tensor core fills the other TMEM stage.
 //
-// One persistent CTA per SM, 320 threads:
-//   warp 0     TMA producer: A tile 128x128 B, B tile 256x128 B per K block
-//              (two 128-row boxes: gate rows + up rows for the SwiGLU epilogue,
-//              or two consecutive N blocks otherwise), 4-stage ring
-//   warp 1     owns TMEM (512 columns = 2 stages x 256 f32 columns), issues
-//              4 x tcgen05.mma.kind::f8f6f4 (M128 N256 K32) per K block
-//   warps 2-9  promotion + epilogue; warp w reads TMEM lanes 32*(w%4)..+31 and
-//              64 gate + 64 up (or 64 + 64 plain) columns -> 128 accumulators
+// One persistent CTA per SM, 384 threads = 3 warpgroups:
+//   warp 0      TMA producer: A tile 128x128 B, B tile 256x128 B per K block
+//               (two 128-row boxes: gate rows + up rows for the SwiGLU epilogue,
+//               or two consecutive N blocks otherwise), 4-stage ring
+//   warp 1      owns TMEM (512 columns = 2 stages x 256 f32 columns), issues
+//               4 x tcgen05.mma.kind::f8f6f4 (M128 N256 K32) per K block
+//   warps 2-3   idle (they complete the first warpgroup, which gives its registers away)
+//   warps 4-11  promotion + epilogue; warp w reads TMEM lanes 32*(w%4)..+31 and
+//               64 gate + 64 up (or 64 + 64 plain) columns -> 128 accumulators plus
+//               64 staging registers, so that two 32-column TMEM loads are always in
+//               flight (setmaxnreg: 56 registers for warpgroup 0, 224 for the other two)
 // Tiles are (group, m-tile, n-tile) with n fastest, so CTAs running together
 // share an A tile and walk one expert's weights once through L2.
 //
@@ -34,7 +37,8 @@ constexpr int BM = 128, BN = 256, BK = 128;
 constexpr int kStages = 4;
 constexpr int kAccStages = 2;
 constexpr int kEpiWarps = 8;
-constexpr int kThreads = 64 + kEpiWarps * 32;
+constexpr int kFirstEpiWarp = 4;
+constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
 constexpr uint32_t kABytes = BM * BK;
 constexpr uint32_t kBBytes = BN * BK;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
@@ -170,6 +174,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
   const uint32_t tmem_base = sh->tmem_base;
   const int total_tiles = sh->pref[p.num_groups] * num_n_tiles;
 
+  // Register hand-over: the producer/MMA warpgroup keeps 56 registers per thread, the two
+  // promotion warpgroups grow to 224 (384 x 168 = 128 x 56 + 256 x 224).
+  if (warp < kFirstEpiWarp) {
+    ptx::setmaxnreg_dec<56>();
   if (warp == 0) {
     // ================================ TMA producer ================================
     if (lane == 0) {
@@ -229,9 +237,11 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
         }
       }
     }
+  }
   } else {
     // ========================= promotion + epilogue warps ==========================
-    const int e = warp - 2;
+    ptx::setmaxnreg_inc<224>();
+    const int e = warp - kFirstEpiWarp;
     const int q = warp & 3;              // TMEM lane quarter this warp may read
     const int hsel = e >> 2;             // which 64-column half of each 128-column block
     const int r_in_tile = q * 32 + lane;
@@ -259,25 +269,26 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t tcol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
+        // Two 32-column loads in flight at any time; the stage goes back to the MMA warp as
+        // soon as its last load has landed, before the last FMAs.
+        uint32_t ra[32], rb[32];
+        ptx::tmem_ld32(tcol, ra);
+        ptx::tmem_ld32(tcol + 32, rb);
+        ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          const float sc = half == 0 ? s0 : s1;
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(ra[j]), s0, acc[j]);
+        ptx::tmem_ld32(tcol + 128, ra);
 #pragma unroll
-          for (int c = 0; c < 4; c += 2) {
-            uint32_t r0[16], r1[16];
-            ptx::tmem_ld16(tcol + half * 128 + c * 16, r0);
-            ptx::tmem_ld16(tcol + half * 128 + (c + 1) * 16, r1);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              acc[half * 64 + c * 16 + j] = fmaf(__uint_as_float(r0[j]), sc, acc[half * 64 + c * 16 + j]);
-              acc[half * 64 + (c + 1) * 16 + j] = fmaf(__uint_as_float(r1[j]), sc, acc[half * 64 + (c + 1) * 16 + j]);
-            }
-          }
-        }
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(rb[j]), s0, acc[32 + j]);
+        ptx::tmem_ld32(tcol + 160, rb);
+        ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&sh->tmem_empty[as]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(__uint_as_float(ra[j]), s1, acc[64 + j]);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(__uint_as_float(rb[j]), s1, acc[96 + j]);
         if (++as == kAccStages) { as = 0; aphase ^= 1u; }
       }
       if (!ok) break;

@@ -1,0 +1,55 @@
+"""One rank of the expert-parallel parity check (launched by tests/test_gpu_ep.py).
+
+Every rank routes its own tokens, the fused layer exchanges fp8 records over NCCL, and the
+rank's output is compared with the CPU oracle, which does not depend on the EP degree."""
+import os
+import sys
+from dataclasses import replace
+
+import torch
+import torch.distributed as dist
+
+ROOT = sys.argv[1]
+sys.path.insert(0, ROOT)
+
+from llm_kernels_b200 import workloads as WL                      # noqa: E402
+from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE        # noqa: E402
+from oracle import restate as R                                   # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", device_id=dev)
+    shape = replace(WL.CONFIG3, tokens=96 + 32 * rank, hidden=512, inter=256, experts=32, n_group=4,
+                    topk_group=2, top_k=4)
+    layer = DeepseekV3MoE(WL.make_config(shape, ep_size=world), device=dev).eval()
+    WL.fill_layer_cpu_seeded(layer, shape)
+    x = WL.tokens(shape, rank=rank)
+    y = layer(x.to(dev).view(1, shape.tokens, -1))
+    layer.check_status()
+    torch.cuda.synchronize()
+
+    W, bias = WL.router_params(shape)
+    kw = dict(top_k=shape.top_k, n_group=shape.n_group, topk_group=shape.topk_group, scoring_func=shape.scoring)
+    idx, w = R.gate_forward(x, W, bias, routed_scaling_factor=shape.scaling, **kw)
+    q13, q2 = [], []
+    for e in range(shape.experts):
+        g, u, d = WL.expert_weights_cpu(shape, e)
+        q13.append(R.weight_quant_fp8(torch.cat([g, u], 0)))
+        q2.append(R.weight_quant_fp8(d))
+    y_ref = R.moe_layer_fp8(x, idx, w, torch.stack([a for a, _ in q13]), torch.stack([s for _, s in q13]),
+                            torch.stack([a for a, _ in q2]), torch.stack([s for _, s in q2]), ep_size=world)
+    err = R.rel_fro(y.cpu().view(shape.tokens, -1).float(), y_ref.float())
+    rows = torch.tensor([layer.last_recv_rows, shape.tokens * shape.top_k], device=dev)
+    dist.all_reduce(rows)
+    assert int(rows[0]) == int(rows[1]), "rows are not conserved across the exchange"
+    assert err < 1e-2, f"rank {rank}: rel_fro {err}"
+    print(f"rank {rank} ok rel_fro={err:.2e} recv_rows={layer.last_recv_rows}", flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
