@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tma_host.cuh"
 
 namespace b200moe {
 
@@ -71,6 +72,12 @@ struct GemmParams {
 };
 
 struct Tile { int m0, m_end, expert, nt; };
+
+// The activation tile is fetched with the smallest of four boxes (16/32/64/128 rows) that covers
+// the rows the group still has: a ragged group then moves only its own rows through L2 and the
+// crossbar.  The tensor core still reads 128 rows; the stale ones only feed output rows that are
+// never stored.
+struct RowMaps { CUtensorMap m[4]; };
 
 __device__ __forceinline__ Tile decode_tile(const SharedTail* sh, const GemmParams& p, int t,
                                             int num_n_tiles) {
@@ -122,7 +129,7 @@ __device__ __forceinline__ void store_row64<__half>(__half* dst, const float* v)
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
+gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
                       const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -143,7 +150,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
     sh->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
-    ptx::prefetch_tensormap(&tmap_a);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ptx::prefetch_tensormap(&tmap_a.m[i]);
     ptx::prefetch_tensormap(&tmap_b);
   }
   if (warp == 1) {
@@ -188,14 +196,18 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
         const Tile tl = decode_tile(sh, p, t, num_n_tiles);
         const int brow0 = tl.expert * p.N + (p.swiglu ? tl.nt * 128 : tl.nt * BN);
         const int brow1 = p.swiglu ? tl.expert * p.N + p.N / 2 + tl.nt * 128 : brow0 + 128;
+        const int rows = min(BM, tl.m_end - tl.m0);
+        const int sel = rows <= 16 ? 0 : (rows <= 32 ? 1 : (rows <= 64 ? 2 : 3));
+        const CUtensorMap* ma = &tmap_a.m[sel];
+        const uint32_t bytes = kBBytes + (16u << sel) * BK;
         for (int kb = 0; kb < KB; ++kb) {
           if (!ptx::mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + size_t(stage) * kStageBytes;
           uint8_t* sb = sa + kABytes;
-          ptx::mbar_arrive_expect_tx(&sh->full[stage], kStageBytes);
+          ptx::mbar_arrive_expect_tx(&sh->full[stage], bytes);
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-          ptx::tma_load_2d(sa, &tmap_a, &sh->full[stage], kb * BK, tl.m0);
+          ptx::tma_load_2d(sa, ma, &sh->full[stage], kb * BK, tl.m0);
           ptx::tma_load_2d(sb, &tmap_b, &sh->full[stage], kb * BK, brow0);
           ptx::tma_load_2d(sb + kBBytes / 2, &tmap_b, &sh->full[stage], kb * BK, brow1);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -249,19 +261,36 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
     int as = 0; uint32_t aphase = 0;
     int it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
-      const Tile tl = decode_tile(sh, p, t, num_n_tiles);
-      const int row = tl.m0 + r_in_tile;
-      const int64_t row_ld = min(static_cast<int64_t>(row), p.M_total - 1);
+    // Per-tile scale pointers and the first K block's scales; fetched one tile ahead so that the
+    // global-load latency hides behind the previous tile's epilogue.
+    struct ScaleCursor { const float* as_ptr; const float* bs0_ptr; const float* bs1_ptr; float sa, b0, b1; };
+    auto open_tile = [&](const Tile& tl) {
+      ScaleCursor c;
+      const int64_t row_ld = min(static_cast<int64_t>(tl.m0 + r_in_tile), p.M_total - 1);
       const int nb0 = p.swiglu ? tl.nt : min(tl.nt * 2, NB - 1);
       const int nb1 = p.swiglu ? NB / 2 + tl.nt : min(tl.nt * 2 + 1, NB - 1);
-      const float* as_ptr = p.a_s + row_ld * p.a_s_stride;
-      const float* bs0_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb0) * KB;
-      const float* bs1_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb1) * KB;
+      c.as_ptr = p.a_s + row_ld * p.a_s_stride;
+      c.bs0_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb0) * KB;
+      c.bs1_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb1) * KB;
+      c.sa = __ldg(c.as_ptr); c.b0 = __ldg(c.bs0_ptr); c.b1 = __ldg(c.bs1_ptr);
+      return c;
+    };
+    Tile tl_next = {};
+    ScaleCursor cur_next = {};
+    if (static_cast<int>(blockIdx.x) < total_tiles) {
+      tl_next = decode_tile(sh, p, blockIdx.x, num_n_tiles);
+      cur_next = open_tile(tl_next);
+    }
+    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+      const Tile tl = tl_next;
+      const int row = tl.m0 + r_in_tile;
+      const float* as_ptr = cur_next.as_ptr;
+      const float* bs0_ptr = cur_next.bs0_ptr;
+      const float* bs1_ptr = cur_next.bs1_ptr;
+      float sa_n = cur_next.sa, b0_n = cur_next.b0, b1_n = cur_next.b1;
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      float sa_n = __ldg(as_ptr), b0_n = __ldg(bs0_ptr), b1_n = __ldg(bs1_ptr);
       for (int kb = 0; kb < KB; ++kb) {
         const float s0 = sa_n * b0_n, s1 = sa_n * b1_n;
         if (kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
@@ -292,6 +321,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
         if (++as == kAccStages) { as = 0; aphase ^= 1u; }
       }
       if (!ok) break;
+      if (t + static_cast<int>(gridDim.x) < total_tiles) {
+        tl_next = decode_tile(sh, p, t + gridDim.x, num_n_tiles);
+        cur_next = open_tile(tl_next);
+      }
       const bool row_ok = row < tl.m_end;
       if (!p.swiglu) {
 #pragma unroll
@@ -348,56 +381,17 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmap_a,
 }
 
 // ---- host side ---------------------------------------------------------------------------
-using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
-                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
-                              CUtensorMapFloatOOBfill);
-
-static EncodeFn get_encode() {
-  static EncodeFn fn = nullptr;
-  if (!fn) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeFn>(sym);
-  }
-  return fn;
-}
-
-// rows x cols bytes, row stride in bytes, box 128 rows x 128 bytes, 128-byte swizzle.
-static int make_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
-                       uint64_t row_stride) {
-  EncodeFn enc = get_encode();
-  if (!enc) return fail(B200MOE_UNSUPPORTED_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
-  const cuuint64_t dims[2] = {cols, rows};
-  const cuuint64_t strides[1] = {row_stride};
-  const cuuint32_t box[2] = {128, 128};
-  const cuuint32_t estr[2] = {1, 1};
-  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
-                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(B200MOE_BAD_ARG, "cuTensorMapEncodeTiled failed with %d", (int)r);
-  return B200MOE_OK;
-}
-
-static int sm_count_and_check(int* sms) {
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return fail(B200MOE_UNSUPPORTED_DEVICE, "no CUDA device");
-  int major = 0;
-  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-  cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev);
-  if (major != 10) return fail(B200MOE_UNSUPPORTED_DEVICE, "tcgen05 kernels need compute capability 10.x, device has %d.x", major);
-  return B200MOE_OK;
-}
-
 static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParams p, int64_t tiles_hint,
                        cudaStream_t st) {
   int sms = 0;
-  if (int rc = sm_count_and_check(&sms)) return rc;
-  CUtensorMap ma, mb;
-  if (int rc = make_map_u8(&ma, a, static_cast<uint64_t>(p.M_total), static_cast<uint64_t>(p.K), static_cast<uint64_t>(a_stride))) return rc;
-  if (int rc = make_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K), static_cast<uint64_t>(p.K))) return rc;
+  if (int rc = require_sm100(&sms)) return rc;
+  RowMaps ma;
+  CUtensorMap mb;
+  for (int i = 0; i < 4; ++i)
+    if (int rc = make_tensor_map_u8(&ma.m[i], a, static_cast<uint64_t>(p.M_total), static_cast<uint64_t>(p.K),
+                                    static_cast<uint64_t>(a_stride), 16u << i)) return rc;
+  if (int rc = make_tensor_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K),
+                                  static_cast<uint64_t>(p.K), 128)) return rc;
   cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
   int grid = sms;
   if (tiles_hint > 0 && tiles_hint < grid) grid = static_cast<int>(tiles_hint);

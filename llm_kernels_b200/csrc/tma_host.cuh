@@ -1,0 +1,56 @@
+// Host-side creation of TMA tensor maps (cuTensorMapEncodeTiled through the runtime's
+// driver entry point, so the library does not link libcuda).
+#pragma once
+
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace b200moe {
+
+using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                              const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                              CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                              CUtensorMapFloatOOBfill);
+
+inline EncodeFn get_tensor_map_encoder() {
+  static EncodeFn fn = nullptr;
+  if (!fn) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(sym);
+  }
+  return fn;
+}
+
+// Byte matrix rows x cols with the given row stride; box = box_rows x 128 bytes, 128-byte swizzle,
+// out-of-range elements read as zero.
+inline int make_tensor_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
+                              uint64_t row_stride, uint32_t box_rows) {
+  EncodeFn enc = get_tensor_map_encoder();
+  if (!enc) return fail(B200MOE_UNSUPPORTED_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride};
+  const cuuint32_t box[2] = {128, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides,
+                         box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200MOE_BAD_ARG, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return B200MOE_OK;
+}
+
+inline int require_sm100(int* sms) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return fail(B200MOE_UNSUPPORTED_DEVICE, "no CUDA device");
+  int major = 0;
+  cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
+  cudaDeviceGetAttribute(sms, cudaDevAttrMultiProcessorCount, dev);
+  if (major != 10)
+    return fail(B200MOE_UNSUPPORTED_DEVICE, "tcgen05 kernels need compute capability 10.x, device has %d.x", major);
+  return B200MOE_OK;
+}
+
+}  // namespace b200moe
