@@ -219,6 +219,49 @@ B200MOE_API int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byt
                              const int64_t* seg_indptr, const int64_t* weight_indices,
                              int epilogue, int32_t* status_word, void* stream);
 
+/* ===================== int4 weight paths (w4a8, w4a16) ==================== */
+
+/* int4 -> int8 step of the two-level format (weight_dequant_int4_kernel,
+ * quantization/w4a8_kernel.py:44-101; the unpack inside w4a8_gemm_kernel :362-380).
+ * packed int32 [W, N/8, K]: word (n/8, k), field n%8 = q[n,k]
+ * (pack_weights_over_rows, quantization/bitpack.py:9-36); s4, z4 int8 [W, N, K/128].
+ * out int8 [W, N, K] = int8((q - z4) * s4) with int8 wrap-around as in the reference.
+ * N % 8 == 0, K % 128 == 0. */
+B200MOE_API int b200moe_w4a8_expand_int8(const void* packed, const int8_t* s4, const int8_t* z4, void* out,
+                             int64_t W, int64_t N, int64_t K, void* stream);
+
+/* Asymmetric group-128 int4 -> bf16: w = (q - zero) * scale rounded once to bf16.
+ * Extends the symmetric dequantization of the reference's w4a16 kernel
+ * (fast_dequant/simple_marlin/marlin_w4a16_gemm.cu:44-64, utils.py:98-136) with a
+ * zero-point.  packed int32 [rows, K/8]: word k/8, field k%8 = q[row,k]
+ * (pack_weights_over_cols, quantization/bitpack.py:38-67); scale, zero bf16 [rows, K/128].
+ * out bf16 [rows, K].  K % 128 == 0. */
+B200MOE_API int b200moe_w4a16_expand_bf16(const void* packed, const void* scale_bf16, const void* zero_bf16,
+                              void* out_bf16, int64_t rows, int64_t K, void* stream);
+
+/* Grouped int8 x int8 GEMM with 1x128 / 128x128 f32 scales: the grouped form of
+ * w4a8_gemm (quantization/w4a8_kernel.py:317-448) once the weights are int8
+ * (b200moe_w4a8_expand_int8): acc += float(dot_kb in s32) * a_s[m,kb] * b_s[n/128,kb].
+ * Arguments as b200moe_grouped_gemm_fp8 with epilogue 0; a, b are int8. */
+B200MOE_API int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes, const float* a_s,
+                            int64_t a_s_row_stride, const void* b, const float* b_s, void* c,
+                            int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                            int64_t K, int num_groups, int num_weights,
+                            const int64_t* seg_indptr, const int64_t* weight_indices,
+                            int32_t* status_word, void* stream);
+
+/* Grouped bf16 x bf16 GEMM with f32 accumulation in TMEM (the unquantized branch of
+ * grouped_gemm_triton, moe/group_gemm_kernel.py:410-412; used by the w4a16 path after
+ * b200moe_w4a16_expand_bf16).  a bf16 [M_total, K] (row stride in bytes), b bf16
+ * [num_weights, N, K].  epilogue 0: c [M_total, N] f32/f16/bf16.  epilogue 2: SwiGLU
+ * (moe/group_gemm_kernel.py:120-168) fused, b rows [0,N/2) gate and [N/2,N) up,
+ * c bf16 [M_total, N/2].  K % 64 == 0, N % 128 == 0 (epilogue 2: N % 256 == 0). */
+B200MOE_API int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
+                              int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                              int64_t K, int num_groups, int num_weights,
+                              const int64_t* seg_indptr, const int64_t* weight_indices,
+                              int epilogue, int32_t* status_word, void* stream);
+
 /* ========================= quantization/bitpack.py ======================== */
 
 /* pack_weights_over_rows / _cols (quantization/bitpack.py:9-67, 84-149,

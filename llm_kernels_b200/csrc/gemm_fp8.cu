@@ -128,18 +128,41 @@ __device__ __forceinline__ void store_row64<__half>(__half* dst, const float* v)
 
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// Operand kinds.  All three share the pipeline; K is counted in bytes (128 per K block).
+//   kFp8  e4m3 x e4m3 -> f32, per-K-block promotion with f32 scales
+//   kI8   s8 x s8 -> s32,     per-K-block promotion with f32 scales (w4a8 path: weights arrive
+//                             as int8 after the int4 -> int8 step of quantization/w4a8_kernel.py:44-101)
+//   kBf16 bf16 x bf16 -> f32, no scales: the whole K loop accumulates in TMEM and the epilogue
+//                             warps read each tile once (w4a16 path after dequantization)
+enum : int { kFp8 = 0, kI8 = 1, kBf16 = 2 };
+
+template <int KIND>
+__device__ __forceinline__ void umma_kind(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
+  if constexpr (KIND == kFp8) ptx::umma_f8f6f4(d, a, b, idesc, acc);
+  else if constexpr (KIND == kI8) ptx::umma_i8(d, a, b, idesc, acc);
+  else ptx::umma_f16(d, a, b, idesc, acc);
+}
+
+template <int KIND>
+__device__ __forceinline__ float tmem_value(uint32_t r) {
+  if constexpr (KIND == kI8) return __int2float_rn(static_cast<int>(r));
+  else return __uint_as_float(r);
+}
+
+template <int KIND>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
-                      const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
+gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
+                  const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SharedTail* sh = reinterpret_cast<SharedTail*>(smem + size_t(kStages) * kStageBytes);
   volatile int* abort_flag = &sh->abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int KB = p.K / BK;
+  const int KB = p.K / BK;                         // p.K is the K extent in BYTES
+  constexpr bool kPromote = KIND != kBf16;
   const int NB = p.N / 128;
-  const int num_n_tiles = p.swiglu ? (p.N / 2) / 128 : (p.N + BN - 1) / BN;
+  const int num_n_tiles = p.swiglu ? (p.N / 2) / 128 : (p.N + BN - 1) / BN;   // swiglu: 0 plain, 1 -> e4m3 + scales, 2 -> bf16
 
   // ---- setup: barriers, TMEM, group table -----------------------------------------
   if (threadIdx.x == 0) {
@@ -226,14 +249,17 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
   } else if (warp == 1) {
     // ================================ MMA issuer ==================================
     if (lane == 0) {
-      constexpr uint32_t idesc = ptx::umma_idesc(1, 0, 0, BM, BN);
+      // D f32 (1) / s32 (2); operand formats: e4m3 = 0, signed int8 = 1, bf16 = 1
+      constexpr uint32_t idesc = KIND == kFp8 ? ptx::umma_idesc(1, 0, 0, BM, BN)
+                                 : (KIND == kI8 ? ptx::umma_idesc(2, 1, 1, BM, BN) : ptx::umma_idesc(1, 1, 1, BM, BN));
       int stage = 0; uint32_t phase = 0;
       int as = 0; uint32_t aphase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
         for (int kb = 0; kb < KB; ++kb) {
           if (!ptx::mbar_wait(&sh->full[stage], phase, abort_flag)) { ok = false; break; }
-          if (!ptx::mbar_wait(&sh->tmem_empty[as], aphase ^ 1u, abort_flag)) { ok = false; break; }
+          if (kPromote || kb == 0)
+            if (!ptx::mbar_wait(&sh->tmem_empty[as], aphase ^ 1u, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
           const uint32_t sa = ptx::smem_u32(smem + size_t(stage) * kStageBytes);
           const uint64_t adesc = ptx::umma_desc_sw128(sa);
@@ -241,11 +267,13 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
           const uint32_t d = tmem_base + static_cast<uint32_t>(as) * BN;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)   // +32 bytes along K = +2 in the >>4 address field
-            ptx::umma_f8f6f4(d, adesc + 2 * k, bdesc + 2 * k, idesc, k > 0 ? 1u : 0u);
+            umma_kind<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, (k > 0 || (!kPromote && kb > 0)) ? 1u : 0u);
           ptx::umma_commit(&sh->empty[stage]);      // smem slot reusable once the MMAs retire
-          ptx::umma_commit(&sh->tmem_full[as]);     // K-block product ready for promotion
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
-          if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+          if (kPromote || kb == KB - 1) {
+            ptx::umma_commit(&sh->tmem_full[as]);   // K-block product (kBf16: whole tile) ready
+            if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+          }
         }
       }
     }
@@ -265,14 +293,16 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
     // global-load latency hides behind the previous tile's epilogue.
     struct ScaleCursor { const float* as_ptr; const float* bs0_ptr; const float* bs1_ptr; float sa, b0, b1; };
     auto open_tile = [&](const Tile& tl) {
-      ScaleCursor c;
-      const int64_t row_ld = min(static_cast<int64_t>(tl.m0 + r_in_tile), p.M_total - 1);
-      const int nb0 = p.swiglu ? tl.nt : min(tl.nt * 2, NB - 1);
-      const int nb1 = p.swiglu ? NB / 2 + tl.nt : min(tl.nt * 2 + 1, NB - 1);
-      c.as_ptr = p.a_s + row_ld * p.a_s_stride;
-      c.bs0_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb0) * KB;
-      c.bs1_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb1) * KB;
-      c.sa = __ldg(c.as_ptr); c.b0 = __ldg(c.bs0_ptr); c.b1 = __ldg(c.bs1_ptr);
+      ScaleCursor c = {nullptr, nullptr, nullptr, 1.f, 1.f, 1.f};
+      if constexpr (kPromote) {
+        const int64_t row_ld = min(static_cast<int64_t>(tl.m0 + r_in_tile), p.M_total - 1);
+        const int nb0 = p.swiglu ? tl.nt : min(tl.nt * 2, NB - 1);
+        const int nb1 = p.swiglu ? NB / 2 + tl.nt : min(tl.nt * 2 + 1, NB - 1);
+        c.as_ptr = p.a_s + row_ld * p.a_s_stride;
+        c.bs0_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb0) * KB;
+        c.bs1_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb1) * KB;
+        c.sa = __ldg(c.as_ptr); c.b0 = __ldg(c.bs0_ptr); c.b1 = __ldg(c.bs1_ptr);
+      }
       return c;
     };
     Tile tl_next = {};
@@ -291,9 +321,10 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      for (int kb = 0; kb < KB; ++kb) {
+      const int KBp = kPromote ? KB : 1;              // TMEM read-backs per tile
+      for (int kb = 0; kb < KBp; ++kb) {
         const float s0 = sa_n * b0_n, s1 = sa_n * b1_n;
-        if (kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
+        if (kPromote && kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
         // warp-uniform outcome: the TMEM loads below need the whole warp converged
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag))) { ok = false; break; }
         ptx::tc_fence_after_sync();
@@ -305,19 +336,19 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
         ptx::tmem_ld32(tcol + 32, rb);
         ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(__uint_as_float(ra[j]), s0, acc[j]);
+        for (int j = 0; j < 32; ++j) acc[j] = fmaf(tmem_value<KIND>(ra[j]), s0, acc[j]);
         ptx::tmem_ld32(tcol + 128, ra);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(__uint_as_float(rb[j]), s0, acc[32 + j]);
+        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(tmem_value<KIND>(rb[j]), s0, acc[32 + j]);
         ptx::tmem_ld32(tcol + 160, rb);
         ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) ptx::mbar_arrive(&sh->tmem_empty[as]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(__uint_as_float(ra[j]), s1, acc[64 + j]);
+        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(tmem_value<KIND>(ra[j]), s1, acc[64 + j]);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(__uint_as_float(rb[j]), s1, acc[96 + j]);
+        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(tmem_value<KIND>(rb[j]), s1, acc[96 + j]);
         if (++as == kAccStages) { as = 0; aphase ^= 1u; }
       }
       if (!ok) break;
@@ -336,6 +367,19 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
             else if (p.c_dtype == B200MOE_F16) store_row64(reinterpret_cast<__half*>(dst) + col0, acc + half * 64);
             else store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
           }
+        }
+      } else if (p.swiglu == 2) {
+        // SwiGLU with the reference's roundings, written as bf16 (no re-quantization)
+#pragma unroll
+        for (int j = 0; j < 64; ++j) {
+          const float g = bf16r(acc[j]);
+          const float u = bf16r(acc[64 + j]);
+          const float a = bf16r(g * __fdividef(1.0f, 1.0f + __expf(-g)));
+          acc[j] = a * u;
+        }
+        if (row_ok) {
+          uint8_t* dst = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(row) * p.c_stride;
+          store_row64(reinterpret_cast<__nv_bfloat16*>(dst) + tl.nt * 128 + hsel * 64, acc);
         }
       } else {
         // SwiGLU with the reference's roundings (gate/up GEMM output, silu and the
@@ -381,6 +425,7 @@ gemm_fp8_block_kernel(const __grid_constant__ RowMaps tmap_a,
 }
 
 // ---- host side ---------------------------------------------------------------------------
+template <int KIND>
 static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParams p, int64_t tiles_hint,
                        cudaStream_t st) {
   int sms = 0;
@@ -392,11 +437,11 @@ static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParam
                                     static_cast<uint64_t>(a_stride), 16u << i)) return rc;
   if (int rc = make_tensor_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K),
                                   static_cast<uint64_t>(p.K), 128)) return rc;
-  cudaFuncSetAttribute(gemm_fp8_block_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+  cudaFuncSetAttribute(gemm_block_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
   int grid = sms;
   if (tiles_hint > 0 && tiles_hint < grid) grid = static_cast<int>(tiles_hint);
-  gemm_fp8_block_kernel<<<grid, kThreads, kSmemBytes, st>>>(ma, mb, p);
-  return check_launch("gemm_fp8_block");
+  gemm_block_kernel<KIND><<<grid, kThreads, kSmemBytes, st>>>(ma, mb, p);
+  return check_launch("gemm_block_kernel");
 }
 
 }  // namespace b200moe
@@ -419,7 +464,7 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
   GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
                static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
-  return launch_gemm(a, K, b, p, tiles, as_stream(stream));
+  return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
 }
 
 extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_bytes, const float* a_s,
@@ -454,5 +499,63 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
                num_weights, c_dtype, epilogue, status_word};
-  return launch_gemm(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+  return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+}
+
+// ---- int8 x int8 (w4a8 after the int4 -> int8 step) and bf16 x bf16 (w4a16 after dequantization) ----
+static int check_grouped_common(const char* who, const void* a, const void* b, const void* c,
+                                const int64_t* seg, int64_t a_stride, int64_t kbytes, int64_t M_total,
+                                int64_t N, int num_groups, int num_weights) {
+  B200MOE_REQUIRE(a && b && c && seg, B200MOE_BAD_ARG, "%s: null pointer", who);
+  B200MOE_REQUIRE(M_total >= 0 && M_total < (int64_t(1) << 31) && N > 0 && N % 128 == 0 && kbytes > 0 && kbytes % 128 == 0,
+                  B200MOE_BAD_SHAPE, "%s: M=%lld N=%lld (N must be a multiple of 128, K of 128 bytes)", who,
+                  (long long)M_total, (long long)N);
+  B200MOE_REQUIRE(num_groups >= 1 && num_groups <= kMaxGroups && num_weights >= 1 &&
+                  static_cast<int64_t>(num_weights) * N < (int64_t(1) << 31), B200MOE_BAD_SHAPE,
+                  "%s: num_groups=%d (max %d) num_weights=%d", who, num_groups, kMaxGroups, num_weights);
+  B200MOE_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(c, 16) && a_stride % 16 == 0 && a_stride >= kbytes,
+                  B200MOE_BAD_ALIGN, "%s: pointers and row strides must be 16-byte aligned", who);
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes, const float* a_s,
+                                       int64_t a_s_row_stride, const void* b, const float* b_s, void* c,
+                                       int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                                       int64_t K, int num_groups, int num_weights,
+                                       const int64_t* seg_indptr, const int64_t* weight_indices,
+                                       int32_t* status_word, void* stream) {
+  if (int rc = check_grouped_common("grouped_gemm_i8", a, b, c, seg_indptr, a_row_stride_bytes, K, M_total, N,
+                                    num_groups, num_weights)) return rc;
+  B200MOE_REQUIRE(a_s && b_s && a_s_row_stride >= K / 128, B200MOE_BAD_ARG, "grouped_gemm_i8: scales");
+  B200MOE_REQUIRE(c_dtype == B200MOE_F32 || c_dtype == B200MOE_F16 || c_dtype == B200MOE_BF16, B200MOE_BAD_DTYPE,
+                  "grouped_gemm_i8: c dtype %d", c_dtype);
+  B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0 && c_row_stride_bytes >= N * (c_dtype == B200MOE_F32 ? 4 : 2),
+                  B200MOE_BAD_ARG, "grouped_gemm_i8: c row stride");
+  if (M_total == 0) return B200MOE_OK;
+  GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
+               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word};
+  return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+}
+
+extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
+                                         int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                                         int64_t K, int num_groups, int num_weights,
+                                         const int64_t* seg_indptr, const int64_t* weight_indices,
+                                         int epilogue, int32_t* status_word, void* stream) {
+  if (int rc = check_grouped_common("grouped_gemm_bf16", a, b, c, seg_indptr, a_row_stride_bytes, 2 * K, M_total, N,
+                                    num_groups, num_weights)) return rc;
+  B200MOE_REQUIRE(epilogue == 0 || epilogue == 2, B200MOE_BAD_ARG, "grouped_gemm_bf16: epilogue %d (0 plain, 2 SwiGLU)", epilogue);
+  if (epilogue == 2) {
+    B200MOE_REQUIRE(N % 256 == 0 && c_dtype == B200MOE_BF16 && c_row_stride_bytes >= N, B200MOE_BAD_ARG,
+                    "grouped_gemm_bf16: the SwiGLU epilogue needs N %% 256 == 0 and a bf16 [M, N/2] output");
+  } else {
+    B200MOE_REQUIRE(c_dtype == B200MOE_F32 || c_dtype == B200MOE_F16 || c_dtype == B200MOE_BF16, B200MOE_BAD_DTYPE,
+                    "grouped_gemm_bf16: c dtype %d", c_dtype);
+    B200MOE_REQUIRE(c_row_stride_bytes >= N * (c_dtype == B200MOE_F32 ? 4 : 2), B200MOE_BAD_ARG, "grouped_gemm_bf16: c row stride");
+  }
+  B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0, B200MOE_BAD_ALIGN, "grouped_gemm_bf16: c row stride alignment");
+  if (M_total == 0) return B200MOE_OK;
+  GemmParams p{nullptr, 0, nullptr, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
+               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word};
+  return launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }

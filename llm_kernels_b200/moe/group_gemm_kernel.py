@@ -149,6 +149,38 @@ def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, ep
     return c
 
 
+def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=None):
+    """tcgen05 grouped int8 GEMM with blockwise f32 scales (the w4a8 path once the weights are
+    int8).  a int8 [M,K], a_s f32 [M,K/128], b int8 [W,N,K], b_s f32 [W,N/128,K/128]."""
+    N.require_cuda(a, a_s, b, b_s, c)
+    assert a.dtype == torch.int8 and b.dtype == torch.int8 and a_s.dtype == torch.float32 and b_s.dtype == torch.float32
+    assert b.is_contiguous() and b_s.is_contiguous() and a.stride(1) == 1 and a_s.stride(1) == 1
+    M, K = a.shape
+    W, Nn, Kb = b.shape
+    assert Kb == K
+    N.check(N.lib().b200moe_grouped_gemm_i8(
+        N.ptr(a), a.stride(0), N.ptr(a_s), a_s.stride(0), N.ptr(b), N.ptr(b_s), N.ptr(c), N.dtype_code(c.dtype),
+        c.stride(0) * c.element_size(), M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr),
+        N.ptr(weight_indices), N.ptr(status_word), N.stream()))
+    return c
+
+
+def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, status_word=None):
+    """tcgen05 grouped bf16 GEMM (reference: the scale-free branch of grouped_gemm_triton, :410-412).
+    epilogue 0: c [M,N]; epilogue 2: SwiGLU fused, c bf16 [M,N/2]."""
+    N.require_cuda(a, b, c)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert b.is_contiguous() and a.stride(1) == 1
+    M, K = a.shape
+    W, Nn, Kb = b.shape
+    assert Kb == K
+    N.check(N.lib().b200moe_grouped_gemm_bf16(
+        N.ptr(a), a.stride(0) * 2, N.ptr(b), N.ptr(c), N.dtype_code(c.dtype), c.stride(0) * c.element_size(),
+        M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices), epilogue,
+        N.ptr(status_word), N.stream()))
+    return c
+
+
 def grouped_gemm_triton(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, batch_size: int,
                         weight_column_major: bool, seg_indptr: Optional[torch.Tensor] = None,
                         weight_indices: Optional[torch.Tensor] = None, use_fp8_w8a8: bool = False,
@@ -159,7 +191,13 @@ def grouped_gemm_triton(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, batch
     (the reference does it with its int8 quantizer, :459-469); pass an e4m3 `a` together
     with scale_a to skip that."""
     assert weight_column_major == True  # noqa: E712  (same assert as the reference)
-    assert block_shape is not None and list(block_shape) == [128, 128], "only block_shape=[128,128] is supported"
+    assert seg_indptr is not None
+    if block_shape is None:
+        # scale-free branch (:410-412): bf16 operands, f32 accumulation
+        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "the unquantized branch takes bfloat16"
+        seg = seg_indptr if seg_indptr.is_contiguous() else seg_indptr.contiguous()
+        return grouped_gemm_bf16(a, b, seg[: batch_size + 1], weight_indices, c, epilogue=0)
+    assert list(block_shape) == [128, 128], "only block_shape=[128,128] is supported"
     assert b.dtype == torch.float8_e4m3fn, "the B200 grouped GEMM takes e4m3 weights"
     assert seg_indptr is not None
     if a.dtype != torch.float8_e4m3fn:

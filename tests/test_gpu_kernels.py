@@ -373,3 +373,80 @@ def test_grouped_gemm_fp8_swiglu_epilogue(dev, counts, I, K, W):
     assert R.rel_fro(got, want) < 5e-3
     torch.testing.assert_close(hs.cpu(), so, rtol=1e-2, atol=0)
     assert float((hq.cpu() != ho.view(torch.uint8)).float().mean()) < 0.01
+
+
+# ---------------------------------------------------------------- int4 weight paths
+def test_w4a8_weight_quant_expand_and_gemm_match_reference_vectors(dev, golden):
+    from llm_kernels_b200.quantization import w4a8_kernel
+    c = golden.case("w4a8")
+    packed, s, s4, z4 = w4a8_kernel.weight_quant(t(c["w"]).to(dev))
+    assert torch.equal(packed.cpu(), t(c["packed"]))
+    assert torch.equal(s.cpu(), t(c["s"], torch.float16))
+    assert torch.equal(s4.cpu(), t(c["s4"])) and torch.equal(z4.cpu(), t(c["z4"]))
+    w8 = w4a8_kernel.expand_int8(packed, s4, z4)
+    assert torch.equal(w8.cpu(), R.w4a8_weight_int8(t(c["packed"]), t(c["s4"]), t(c["z4"])))
+    deq = w4a8_kernel.weight_dequant(packed, s, s4, z4)
+    assert torch.equal(deq.cpu(), t(c["dequant"], torch.float16))
+    a8, a8s = w4a8_kernel.act_quant(t(c["x"]).to(dev))
+    out = w4a8_kernel.w4a8_gemm(a8, a8s, packed, s, s4, z4, out_dtype=torch.float32)
+    # int8 dots are exact; only the f32 accumulation order of the K blocks differs
+    assert R.rel_fro(out.cpu(), t(c["c"])) < 1e-6
+
+
+@pytest.mark.parametrize("counts,N,K,W", [([5, 0, 65, 27], 256, 256, 4), ([300, 129], 384, 1024, 2)])
+def test_grouped_gemm_i8(dev, counts, N, K, W):
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    g = torch.Generator().manual_seed(41)
+    M = sum(counts)
+    a = torch.randint(-127, 128, (M, K), generator=g, dtype=torch.int32).to(torch.int8)
+    b = torch.randint(-119, 120, (W, N, K), generator=g, dtype=torch.int32).to(torch.int8)
+    a_s = torch.rand(M, K // 128, generator=g) * 0.01 + 1e-3
+    b_s = torch.rand(W, N // 128, K // 128, generator=g) * 0.01 + 1e-3
+    seg = torch.zeros(len(counts) + 1, dtype=torch.int64); seg[1:] = torch.cumsum(torch.tensor(counts), 0)
+    c = torch.full((M, N), float("nan"), dtype=torch.float32, device=dev)
+    G.grouped_gemm_i8(a.to(dev), a_s.to(dev), b.to(dev), b_s.to(dev), seg.to(dev), None, c)
+    ref = torch.zeros(M, N)
+    for gi in range(len(counts)):
+        m0, m1 = int(seg[gi]), int(seg[gi + 1])
+        for kb in range(K // 128):
+            ks = slice(kb * 128, (kb + 1) * 128)
+            d = (a[m0:m1, ks].double() @ b[gi][:, ks].double().t()).float()
+            ref[m0:m1] += d * a_s[m0:m1, kb:kb + 1] * b_s[gi].repeat_interleave(128, 0)[:, kb].unsqueeze(0)
+    assert R.rel_fro(c.cpu(), ref) < 1e-6
+
+
+def test_w4a16_quant_expand_and_gemm(dev):
+    from llm_kernels_b200.quantization import w4a16_kernel
+    g = torch.Generator().manual_seed(43)
+    w = torch.randn(384, 512, generator=g) * 0.02
+    packed, sc, z = w4a16_kernel.weight_quant(w.to(dev))
+    qo, so, zo = R.w4a16_quantize_asym(w)
+    assert torch.equal(sc.cpu(), so) and torch.equal(z.cpu(), zo)
+    assert torch.equal(packed.cpu(), R.pack_weights_over_cols(qo, 4, 32)[0])
+    wd = w4a16_kernel.expand_bf16(packed, sc, z)
+    assert torch.equal(wd.cpu(), R.w4a16_dequant(qo, so, zo))           # bit-exact bf16
+    a = torch.randn(200, 512, generator=g).to(torch.bfloat16)
+    c = w4a16_kernel.w4a16_gemm(a.to(dev), packed, sc, z, out_dtype=torch.float32)
+    ref = a.float() @ R.w4a16_dequant(qo, so, zo).float().t()
+    # same bf16 operands, f32 accumulation: tolerance of the w4a16 path (3e-3) with a wide margin
+    assert R.rel_fro(c.cpu(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("counts,I,K,W", [([5, 0, 65, 27], 128, 256, 4), ([200, 130], 256, 512, 2)])
+def test_grouped_gemm_bf16_plain_and_swiglu(dev, counts, I, K, W):
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    g = torch.Generator().manual_seed(47)
+    M = sum(counts)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    b = (torch.randn(W, 2 * I, K, generator=g) * 0.05).to(torch.bfloat16)
+    seg = torch.zeros(len(counts) + 1, dtype=torch.int64); seg[1:] = torch.cumsum(torch.tensor(counts), 0)
+    widx = torch.arange(W, dtype=torch.int64)
+    ref = R.grouped_gemm_plain(a, b, seg, widx, out_dtype=torch.float32)
+    c = torch.zeros(M, 2 * I, dtype=torch.bfloat16, device=dev)
+    G.grouped_gemm_bf16(a.to(dev), b.to(dev), seg.to(dev), None, c, epilogue=0)
+    assert R.rel_fro(c.cpu().float(), ref) < 3e-3                      # bf16 output rounding
+    h = torch.zeros(M, I, dtype=torch.bfloat16, device=dev)
+    G.grouped_gemm_bf16(a.to(dev), b.to(dev), seg.to(dev), None, h, epilogue=2)
+    want = torch.empty(M, I, dtype=torch.bfloat16)
+    R.silu_and_mul(ref.to(torch.bfloat16), torch.zeros(M, dtype=torch.long), None, 0, 0, want)
+    assert R.rel_fro(h.cpu().float(), want.float()) < 3e-3
