@@ -166,6 +166,16 @@ B200MOE_API int b200moe_permute_quant_fp8(const void* x, int x_dtype, const int3
                               void* out_q, int64_t out_q_row_stride_bytes,
                               float* out_s, int64_t out_s_row_stride, void* stream);
 
+/* Same fusion with the int8 per-token-group quantizer (s = amax/127; rounding as in
+ * b200moe_act_quant_int8).  The scale is rounded to f16 as the reference stores it
+ * (quantization/w4a8_kernel.py:163-168) and written as f32 so that the payload record can
+ * be fed to b200moe_grouped_gemm_i8 directly. */
+B200MOE_API int b200moe_permute_quant_int8(const void* x, int x_dtype, const int32_t* src2dst,
+                               const int64_t* topk_ids, int start_expert_id, int end_expert_id,
+                               int64_t T, int topk, int64_t H,
+                               void* out_q, int64_t out_q_row_stride_bytes,
+                               float* out_s, int64_t out_s_row_stride, int rounding, void* stream);
+
 /* silu_and_mul_triton_kernel / gelu_and_mul_triton_kernel
  * (moe/group_gemm_kernel.py:120-168, 176-235).  gateup [rows, two_I] =
  * [gate | up]; rows whose reorder_topk_ids is outside [start,end] are skipped

@@ -38,6 +38,7 @@ SIGNATURES = {
     "b200moe_route_metadata_noalloc": (_i, [_p, _i64, _i, _p, _p, _p, _p]),
     "b200moe_pre_reorder": (_i, [_p, _i, _p, _i, _p, _p, _p, _i, _i, _i64, _i, _i64, _p]),
     "b200moe_permute_quant_fp8": (_i, [_p, _i, _p, _p, _i, _i, _i64, _i, _i64, _p, _i64, _p, _i64, _p]),
+    "b200moe_permute_quant_int8": (_i, [_p, _i, _p, _p, _i, _i, _i64, _i, _i64, _p, _i64, _p, _i64, _i, _p]),
     "b200moe_act_and_mul": (_i, [_p, _i, _p, _i, _i64, _i64, _p, _p, _i, _i, _i, _p]),
     "b200moe_post_reorder": (_i, [_p, _i, _p, _p, _p, _p, _i, _i, _i64, _i, _i64, _p]),
     "b200moe_grouped_gemm_fp8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _p, _i64,

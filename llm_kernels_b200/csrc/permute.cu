@@ -92,6 +92,50 @@ __global__ void __launch_bounds__(256) permute_quant_fp8_kernel(
   }
 }
 
+// Same with the int8 quantizer of quantization/w4a8_kernel.py:145-168 (rounding 1 = floor(v+0.5))
+// or quantization/int8_kernel.py:9-31 (rounding 0 = half away from zero): s = amax/127 rounded to
+// f16 as the reference stores it, written out as f32 next to the payload.
+template <typename TI>
+__global__ void __launch_bounds__(256) permute_quant_int8_kernel(
+    const TI* __restrict__ x, const int32_t* __restrict__ src2dst,
+    const int64_t* __restrict__ topk_ids, int lo, int hi, int topk, int64_t H,
+    int8_t* __restrict__ out_q, int64_t q_stride, float* __restrict__ out_s, int64_t s_stride,
+    int rounding) {
+  __shared__ int32_t s_dst[kMaxK], s_exp[kMaxK];
+  const int64_t t = blockIdx.x;
+  const int n = load_slots(src2dst, topk_ids, t, topk, lo, hi, s_dst, s_exp);
+  if (n == 0) return;
+  const int64_t chunks = H / 8;
+  const int64_t padded = (chunks + 31) & ~int64_t(31);
+  for (int64_t i = threadIdx.x; i < padded; i += blockDim.x) {
+    const bool live = i < chunks;
+    float v[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    if (live) load8(x + t * H + i * 8, v);
+    float amax = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) amax = fmaxf(amax, fabsf(v[k]));
+#pragma unroll
+    for (int o = 8; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!live) continue;
+    const float scale = __fdiv_rn(amax, 127.f);
+    uint2 packed;
+    int8_t* o8 = reinterpret_cast<int8_t*>(&packed);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float q = __fdiv_rn(v[k], scale);
+      const float rq = rounding == 0 ? roundf(q) : floorf(q + 0.5f);
+      o8[k] = static_cast<int8_t>(__float2int_rz(fminf(fmaxf(rq, -128.f), 127.f)));
+    }
+    const float stored = __half2float(__float2half_rn(scale));
+    const bool lead = (threadIdx.x & 15) == 0;
+    for (int j = 0; j < n; ++j) {
+      const int64_t d = s_dst[j];
+      *reinterpret_cast<uint2*>(out_q + d * q_stride + i * 8) = packed;
+      if (lead) out_s[d * s_stride + i / 16] = stored;
+    }
+  }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(256) act_and_mul_kernel(
     const T* __restrict__ gateup, T* __restrict__ out, int64_t two_I,
@@ -221,6 +265,34 @@ extern "C" int b200moe_permute_quant_fp8(const void* x, int x_dtype, const int32
   DISPATCH_16BIT_OR_F32(x_dtype, LAUNCH_PQ)
 #undef LAUNCH_PQ
   return check_launch("permute_quant_fp8");
+}
+
+extern "C" int b200moe_permute_quant_int8(const void* x, int x_dtype, const int32_t* src2dst,
+                                          const int64_t* topk_ids, int start_expert_id,
+                                          int end_expert_id, int64_t T, int topk, int64_t H,
+                                          void* out_q, int64_t out_q_row_stride_bytes,
+                                          float* out_s, int64_t out_s_row_stride, int rounding,
+                                          void* stream) {
+  B200MOE_REQUIRE(x && out_q && out_s && src2dst && topk_ids, B200MOE_BAD_ARG, "permute_quant_int8: null pointer");
+  B200MOE_REQUIRE(T >= 0 && H > 0 && H % 128 == 0, B200MOE_BAD_SHAPE,
+                  "permute_quant_int8: hidden_size=%lld must be divisible by block_size (block_size=128)", (long long)H);
+  B200MOE_REQUIRE(topk >= 1 && topk <= kMaxK, B200MOE_BAD_SHAPE, "permute_quant_int8: topk=%d", topk);
+  B200MOE_REQUIRE(rounding == 0 || rounding == 1, B200MOE_BAD_ARG, "permute_quant_int8: rounding %d", rounding);
+  B200MOE_REQUIRE(aligned(x, 16) && aligned(out_q, 8) && out_q_row_stride_bytes % 8 == 0 && aligned(out_s, 4),
+                  B200MOE_BAD_ALIGN, "permute_quant_int8: alignment");
+  B200MOE_REQUIRE(out_q_row_stride_bytes >= H && out_s_row_stride >= H / 128, B200MOE_BAD_ARG,
+                  "permute_quant_int8: output strides smaller than a row");
+  if (T == 0) return B200MOE_OK;
+  cudaStream_t st = as_stream(stream);
+  const int th = pick_threads(H / 8);
+  const unsigned grid = static_cast<unsigned>(T);
+#define LAUNCH_PQ8(TI)                                                                           \
+  permute_quant_int8_kernel<TI><<<grid, th, 0, st>>>(static_cast<const TI*>(x), src2dst, topk_ids, \
+      start_expert_id, end_expert_id, topk, H, static_cast<int8_t*>(out_q),                       \
+      out_q_row_stride_bytes, out_s, out_s_row_stride, rounding)
+  DISPATCH_16BIT_OR_F32(x_dtype, LAUNCH_PQ8)
+#undef LAUNCH_PQ8
+  return check_launch("permute_quant_int8");
 }
 
 extern "C" int b200moe_act_and_mul(const void* gateup, int dtype, void* down_input, int out_dtype,

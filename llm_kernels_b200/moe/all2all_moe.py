@@ -26,7 +26,7 @@ import torch.distributed as dist
 from torch import nn
 
 from .. import _native as N
-from ..quantization import fp8_kernel
+from ..quantization import fp8_kernel, w4a8_kernel, w4a16_kernel
 from . import ep_comm
 from . import group_gemm_kernel as G
 from .config import Config  # noqa: F401  (re-exported like the reference does)
@@ -84,14 +84,26 @@ class MoEGate(nn.Module):
 
 
 class DeepseekV3MoE(nn.Module):
-    """A mixed expert module (reference :120-286) over quantized fused expert weights."""
+    """A mixed expert module (reference :120-286) over quantized fused expert weights.
+
+    config.quantize_method selects the expert path:
+      "fp8_block"  e4m3 weights, 128x128 f32 scales; activations e4m3 1x128 (dispatch payload:
+                   e4m3 row + f32 scales in one record); GEMM-1 fuses SwiGLU + re-quantization
+      "w4a16"      asymmetric group-128 int4 weights (bf16 scale/zero); bf16 activations
+                   (dispatch payload: bf16 rows); GEMM-1 fuses SwiGLU
+      "w4a8"       two-level int4 weights of quantization/w4a8_kernel.py; int8 activations
+                   1x128 with f16 scales (dispatch payload: int8 row + scales in one record)
+    """
+
+    METHODS = ("fp8_block", "w4a16", "w4a8")
 
     def __init__(self, config, device=None):
         super().__init__()
         self.config = config
         self.num_experts_per_tok = config.num_experts_per_tok
-        if getattr(config, "quantize_method", "fp8_block") != "fp8_block":
-            raise NotImplementedError(f"quantize_method {config.quantize_method!r}")
+        self.method = getattr(config, "quantize_method", "fp8_block")
+        if self.method not in self.METHODS:
+            raise NotImplementedError(f"quantize_method {self.method!r}")
         if getattr(config, "hidden_act", "silu") != "silu":
             raise NotImplementedError("the fused GEMM-1 epilogue implements silu")
         if hasattr(config, "ep_size") and config.ep_size > 1:
@@ -106,12 +118,31 @@ class DeepseekV3MoE(nn.Module):
         self.experts_per_rank = E // self.ep_size
         El = self.experts_per_rank
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        f8 = torch.float8_e4m3fn
+        self._dev = dev
         reg = lambda name, t: self.register_buffer(name, t, persistent=True)
-        reg("w13_weight", torch.zeros(El, 2 * I, H, dtype=f8, device=dev))
-        reg("w13_weight_scale", torch.ones(El, 2 * I // 128, H // 128, dtype=torch.float32, device=dev))
-        reg("w2_weight", torch.zeros(El, H, I, dtype=f8, device=dev))
-        reg("w2_weight_scale", torch.ones(El, H // 128, I // 128, dtype=torch.float32, device=dev))
+        z = lambda *shape, dtype: torch.zeros(*shape, dtype=dtype, device=dev)
+        if self.method == "fp8_block":
+            f8 = torch.float8_e4m3fn
+            reg("w13_weight", z(El, 2 * I, H, dtype=f8))
+            reg("w13_weight_scale", torch.ones(El, 2 * I // 128, H // 128, dtype=torch.float32, device=dev))
+            reg("w2_weight", z(El, H, I, dtype=f8))
+            reg("w2_weight_scale", torch.ones(El, H // 128, I // 128, dtype=torch.float32, device=dev))
+        elif self.method == "w4a16":
+            reg("w13_qweight", z(El, 2 * I, H // 8, dtype=torch.int32))
+            reg("w13_scale", z(El, 2 * I, H // 128, dtype=torch.bfloat16))
+            reg("w13_zero", z(El, 2 * I, H // 128, dtype=torch.bfloat16))
+            reg("w2_qweight", z(El, H, I // 8, dtype=torch.int32))
+            reg("w2_scale", z(El, H, I // 128, dtype=torch.bfloat16))
+            reg("w2_zero", z(El, H, I // 128, dtype=torch.bfloat16))
+        else:
+            reg("w13_qweight", z(El, 2 * I // 8, H, dtype=torch.int32))
+            reg("w13_weight_scale", z(El, 2 * I // 128, H // 128, dtype=torch.float32))
+            reg("w13_s4", z(El, 2 * I, H // 128, dtype=torch.int8))
+            reg("w13_z4", z(El, 2 * I, H // 128, dtype=torch.int8))
+            reg("w2_qweight", z(El, H // 8, I, dtype=torch.int32))
+            reg("w2_weight_scale", z(El, H // 128, I // 128, dtype=torch.float32))
+            reg("w2_s4", z(El, H, I // 128, dtype=torch.int8))
+            reg("w2_z4", z(El, H, I // 128, dtype=torch.int8))
         self.gate = MoEGate(config).to(dev)
         if config.n_shared_experts:
             raise NotImplementedError("shared experts are not built yet")
@@ -132,24 +163,38 @@ class DeepseekV3MoE(nn.Module):
     @torch.no_grad()
     def load_expert(self, local_idx: int, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor):
         """Quantizes one expert's nn.Linear weights (gate/up [I,H], down [H,I], the layout of
-        DeepseekV3MLP, reference :13-29) into the fused e4m3 tensors."""
+        DeepseekV3MLP, reference :13-29) into the fused tensors of the configured method."""
         w13 = torch.cat([gate_w, up_w], dim=0).contiguous()
-        q, s = fp8_kernel.weight_quant(w13)
-        self.w13_weight[local_idx].copy_(q)
-        self.w13_weight_scale[local_idx].copy_(s)
-        q, s = fp8_kernel.weight_quant(down_w.contiguous())
-        self.w2_weight[local_idx].copy_(q)
-        self.w2_weight_scale[local_idx].copy_(s)
+        w2 = down_w.contiguous()
+        if self.method == "fp8_block":
+            q, s = fp8_kernel.weight_quant(w13)
+            self.w13_weight[local_idx].copy_(q)
+            self.w13_weight_scale[local_idx].copy_(s)
+            q, s = fp8_kernel.weight_quant(w2)
+            self.w2_weight[local_idx].copy_(q)
+            self.w2_weight_scale[local_idx].copy_(s)
+        elif self.method == "w4a16":
+            for name, w in (("w13", w13), ("w2", w2)):
+                packed, sc, zp = w4a16_kernel.weight_quant(w)
+                getattr(self, f"{name}_qweight")[local_idx].copy_(packed)
+                getattr(self, f"{name}_scale")[local_idx].copy_(sc)
+                getattr(self, f"{name}_zero")[local_idx].copy_(zp)
+        else:
+            for name, w in (("w13", w13), ("w2", w2)):
+                packed, s, s4, z4 = w4a8_kernel.weight_quant(w.float().contiguous())
+                getattr(self, f"{name}_qweight")[local_idx].copy_(packed)
+                getattr(self, f"{name}_weight_scale")[local_idx].copy_(s.float())
+                getattr(self, f"{name}_s4")[local_idx].copy_(s4)
+                getattr(self, f"{name}_z4")[local_idx].copy_(z4)
 
     def _buf(self, name, shape, dtype):
-        key = name
-        t = self._buffers_cache.get(key)
+        t = self._buffers_cache.get(name)
         n = 1
         for d in shape:
             n *= d
         if t is None or t.dtype != dtype or t.numel() < n:
-            t = torch.empty(max(n, 1), dtype=dtype, device=self.w13_weight.device)
-            self._buffers_cache[key] = t
+            t = torch.empty(max(n, 1), dtype=dtype, device=self._dev)
+            self._buffers_cache[name] = t
         return t[:n].view(*shape)
 
     # ---- forward ---------------------------------------------------------------------
@@ -169,28 +214,38 @@ class DeepseekV3MoE(nn.Module):
     def moe_infer(self, x, topk_ids, topk_weight):
         return self.triton_group_gemm_moe_infer(x, topk_ids, topk_weight)
 
+    def _record_bytes(self, H):
+        """Bytes of one dispatched row: payload, then f32 scales, padded to 16 (TMA row alignment)."""
+        if self.method == "w4a16":
+            return 2 * H
+        return (H + (H // 128) * 4 + 15) // 16 * 16
+
     @torch.no_grad()
     def triton_group_gemm_moe_infer(self, x, topk_ids, topk_weight):
         """The fused expert-parallel pipeline (finishes the stub at reference :282-286)."""
         cfg = self.config
         T, H = x.shape
         k = topk_ids.shape[1]
-        I = cfg.moe_intermediate_size
         E = cfg.n_routed_experts
         S = T * k
         assert x.dtype == torch.bfloat16, "activations must be bfloat16"
         reorder_ids, src2dst, seg_indptr = G.run_moe_ep_preproess(topk_ids, E)
         self._mark("route_metadata")
-        # packed record: e4m3 row + f32 scales, padded so rows stay 16-byte aligned for TMA
-        rec = (H + (H // 128) * 4 + 15) // 16 * 16
+        rec = self._record_bytes(H)
         send = self._buf("send", (S, rec), torch.uint8)
-        send_q = send[:, :H]
-        send_s = send[:, H:H + (H // 128) * 4].view(torch.float32)
-        G.permute_quant_fp8(x, src2dst, topk_ids, 0, E - 1, send_q, send_s)
+        if self.method == "fp8_block":
+            G.permute_quant_fp8(x, src2dst, topk_ids, 0, E - 1, send[:, :H],
+                                send[:, H:H + (H // 128) * 4].view(torch.float32))
+        elif self.method == "w4a8":
+            G.permute_quant_int8(x, src2dst, topk_ids, 0, E - 1, send[:, :H],
+                                 send[:, H:H + (H // 128) * 4].view(torch.float32), rounding="floor_half")
+        else:
+            G.pre_reorder_triton_kernel[(T,)](x, send.view(torch.bfloat16), src2dst, topk_ids, None, 0, E - 1, k, H,
+                                              BLOCK_SIZE=512)
         self._mark("permute_quant")
 
         if self.ep_size == 1:
-            a_q, a_s, rows = send_q, send_s, S
+            rows_buf, rows = send, S
             seg, widx = seg_indptr, None
         else:
             # Received rows stay ordered by (source rank, local expert); each such run is one
@@ -198,23 +253,15 @@ class DeepseekV3MoE(nn.Module):
             # host-side re-sort (:229-240) is not needed.
             plan = ep_comm.plan_exchange(seg_indptr, self.ep_size)
             rows = plan.recv_rows
-            recv = self._buf("recv", (max(rows, 1), rec), torch.uint8)[:rows]
-            ep_comm.dispatch(plan, send, recv)
-            a_q, a_s = recv[:, :H], recv[:, H:H + (H // 128) * 4].view(torch.float32)
+            rows_buf = self._buf("recv", (max(rows, 1), rec), torch.uint8)[:rows]
+            ep_comm.dispatch(plan, send, rows_buf)
             seg, widx = plan.seg_indptr, plan.weight_indices
             self._mark("dispatch_a2a")
         self.last_recv_rows = rows
 
-        h_q = self._buf("h_q", (rows, I), torch.uint8)
-        h_s = self._buf("h_s", (rows, I // 128), torch.float32)
         down = self._buf("down", (rows, H), torch.bfloat16)
         if rows > 0:
-            G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx,
-                               h_q, h_s, epilogue=1, status_word=self._status)
-            self._mark("gemm1_swiglu")
-            G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
-                               down, None, epilogue=0, status_word=self._status)
-            self._mark("gemm2")
+            getattr(self, "_experts_" + self.method)(rows_buf, rows, seg, widx, down)
 
         if self.ep_size > 1:
             back = self._buf("back", (S, H), torch.bfloat16)
@@ -225,6 +272,51 @@ class DeepseekV3MoE(nn.Module):
                                            BLOCK_SIZE=512)
         self._mark("post_reorder")
         return out
+
+    # ---- expert FFNs over the permuted rows ---------------------------------------------
+    def _experts_fp8_block(self, buf, rows, seg, widx, down):
+        H, I = self.config.hidden_size, self.config.moe_intermediate_size
+        a_q, a_s = buf[:, :H], buf[:, H:H + (H // 128) * 4].view(torch.float32)
+        h_q = self._buf("h_q", (rows, I), torch.uint8)
+        h_s = self._buf("h_s", (rows, I // 128), torch.float32)
+        G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx,
+                           h_q, h_s, epilogue=1, status_word=self._status)
+        self._mark("gemm1_swiglu")
+        G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
+                           down, None, epilogue=0, status_word=self._status)
+        self._mark("gemm2")
+
+    def _experts_w4a16(self, buf, rows, seg, widx, down):
+        I = self.config.moe_intermediate_size
+        a = buf.view(torch.bfloat16)
+        w13 = w4a16_kernel.expand_bf16(self.w13_qweight, self.w13_scale, self.w13_zero)
+        self._mark("expand_w13")
+        h = self._buf("h_bf16", (rows, I), torch.bfloat16)
+        G.grouped_gemm_bf16(a, w13, seg, widx, h, epilogue=2, status_word=self._status)
+        self._mark("gemm1_swiglu")
+        del w13
+        w2 = w4a16_kernel.expand_bf16(self.w2_qweight, self.w2_scale, self.w2_zero)
+        self._mark("expand_w2")
+        G.grouped_gemm_bf16(h, w2, seg, widx, down, epilogue=0, status_word=self._status)
+        self._mark("gemm2")
+
+    def _experts_w4a8(self, buf, rows, seg, widx, down):
+        H, I = self.config.hidden_size, self.config.moe_intermediate_size
+        a_q, a_s = buf[:, :H].view(torch.int8), buf[:, H:H + (H // 128) * 4].view(torch.float32)
+        w13 = w4a8_kernel.expand_int8(self.w13_qweight, self.w13_s4, self.w13_z4)
+        self._mark("expand_w13")
+        gu = self._buf("gateup", (rows, 2 * I), torch.bfloat16)
+        G.grouped_gemm_i8(a_q, a_s, w13, self.w13_weight_scale, seg, widx, gu, status_word=self._status)
+        self._mark("gemm1")
+        del w13
+        h = self._buf("h_bf16", (rows, I), torch.bfloat16)
+        G.silu_and_mul_triton_kernel[(rows,)](gu, h, 2 * I, None, None, 0, 0, BLOCK_SIZE=512)
+        h_q, h_s = w4a8_kernel.act_quant(h)
+        self._mark("silu_quant")
+        w2 = w4a8_kernel.expand_int8(self.w2_qweight, self.w2_s4, self.w2_z4)
+        self._mark("expand_w2")
+        G.grouped_gemm_i8(h_q, h_s.float(), w2, self.w2_weight_scale, seg, widx, down, status_word=self._status)
+        self._mark("gemm2")
 
     def check_status(self):
         """Raises if a kernel of an earlier forward reported a device-side timeout (synchronises)."""

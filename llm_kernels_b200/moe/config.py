@@ -26,7 +26,9 @@ class Config:
         self.hidden_act = "silu"
         self.use_triton_group_gemm = True      # the grouped path is the only path here
 
-        # quantization: "fp8_block" = e4m3 weights with 128x128 scales, e4m3 activations 1x128
+        # quantization: "fp8_block" = e4m3 weights with 128x128 scales, e4m3 activations 1x128;
+        # "w4a16" = asymmetric group-128 int4 weights, bf16 activations;
+        # "w4a8" = two-level int4 weights, int8 activations 1x128
         self.quantize_method = "fp8_block"
         self.use_block_quant = True
         self.w_quant_block_size = (128, 128)

@@ -126,6 +126,20 @@ def permute_quant_fp8(x, src2dst, topk_ids, start_expert_id, end_expert_id, out_
                                               N.ptr(out_s), out_s.stride(0), N.stream()))
 
 
+def permute_quant_int8(x, src2dst, topk_ids, start_expert_id, end_expert_id, out_q, out_s, rounding="floor_half"):
+    """Fused pre_reorder (:81-117) + 1x128 int8 act_quant; out_q int8/uint8 view [S, >=H], out_s f32 view
+    [S, >=H/128] (the f16-rounded scale stored as f32)."""
+    N.require_cuda(x, out_q, out_s)
+    T, H = x.shape
+    k = topk_ids.shape[1]
+    assert x.is_contiguous() and out_q.stride(1) == 1 and out_s.stride(1) == 1 and out_s.dtype == torch.float32
+    N.check(N.lib().b200moe_permute_quant_int8(N.ptr(x), N.dtype_code(x.dtype), N.ptr(src2dst), N.ptr(topk_ids),
+                                               int(start_expert_id), int(end_expert_id), T, k, H,
+                                               N.ptr(out_q), out_q.stride(0) * out_q.element_size(),
+                                               N.ptr(out_s), out_s.stride(0),
+                                               {"half_away": 0, "floor_half": 1}[rounding], N.stream()))
+
+
 def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, epilogue: int = 0,
                      status_word=None):
     """tcgen05 grouped blockwise GEMM on already-quantized activations.

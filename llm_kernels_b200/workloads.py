@@ -29,6 +29,7 @@ class LayerShape:
     scaling: float
     seed: int
     zipf_bias: float = 0.0       # strength of the popularity bias (0 = none)
+    method: str = "fp8_block"    # expert quantization (Config.quantize_method)
 
 
 # configs[0]: 512 tokens, H 1024, 8 experts top-2 softmax, SwiGLU 2048, fp8 blockwise
@@ -43,6 +44,13 @@ CONFIG3 = LayerShape("cfg3_dsv3_fp8", 4096, 7168, 2048, 256, 8, 8, 4, "sigmoid",
 CONFIG3_SMALL = LayerShape("cfg3_small", 1024, 7168, 2048, 32, 4, 4, 2, "sigmoid", 2.5, 3, zipf_bias=1.0)
 
 
+# configs[2]: Mixtral shape, 8 experts top-2 softmax, hidden 4096, SwiGLU 14336, w4a16, 8192 tokens/rank
+CONFIG2 = LayerShape("cfg2_mixtral_w4a16", 8192, 4096, 14336, 8, 2, 1, 1, "softmax", 1.0, 2, method="w4a16")
+# configs[4]: decode regime, 64 tokens/rank, 256 experts top-8, hidden 7168, SwiGLU 2048, w4a8,
+# routing uniform over the experts (zero bias, plain top-8 of the sigmoid scores)
+CONFIG4 = LayerShape("cfg4_decode_w4a8", 64, 7168, 2048, 256, 8, 1, 1, "sigmoid", 2.5, 4, method="w4a8")
+
+
 def make_config(shape: LayerShape, ep_size: int = 1) -> Config:
     c = Config()
     c.hidden_size, c.moe_intermediate_size = shape.hidden, shape.inter
@@ -50,6 +58,7 @@ def make_config(shape: LayerShape, ep_size: int = 1) -> Config:
     c.n_group, c.topk_group = shape.n_group, shape.topk_group
     c.scoring_func, c.routed_scaling_factor = shape.scoring, shape.scaling
     c.norm_topk_prob, c.n_shared_experts, c.ep_size = True, 0, ep_size
+    c.quantize_method = shape.method
     return c
 
 
@@ -95,7 +104,7 @@ def expert_weights_cpu(shape: LayerShape, expert: int):
 def fill_layer_cpu_seeded(layer, shape: LayerShape):
     """Loads CPU-seeded weights into a DeepseekV3MoE (small shapes: parity tests)."""
     W, bias = router_params(shape)
-    dev = layer.w13_weight.device
+    dev = layer._dev
     layer.gate.weight.data.copy_(W.to(dev))
     layer.gate.e_score_correction_bias.data.copy_(bias.to(dev))
     for le in range(layer.experts_per_rank):
@@ -107,7 +116,7 @@ def fill_layer_cpu_seeded(layer, shape: LayerShape):
 def fill_layer_gpu(layer, shape: LayerShape):
     """Draws ~N(0, 0.02) expert weights on the GPU, expert by expert (benchmark sizes)."""
     W, bias = router_params(shape)
-    dev = layer.w13_weight.device
+    dev = layer._dev
     layer.gate.weight.data.copy_(W.to(dev))
     layer.gate.e_score_correction_bias.data.copy_(bias.to(dev))
     for le in range(layer.experts_per_rank):

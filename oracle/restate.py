@@ -418,6 +418,71 @@ def moe_layer_fp8(x, topk_ids, topk_weight, w13, w13_s, w2, w2_s, *,
     return y.to(out_dtype)
 
 
+def _permuted_rows(x, topk_ids, num_experts):
+    T, k = topk_ids.shape
+    _, src2dst, seg = run_moe_ep_preproess(topk_ids, num_experts)
+    dst_tok = torch.empty(T * k, dtype=torch.long, device=x.device)
+    dst_tok[src2dst.long()] = torch.arange(T * k, device=x.device) // k
+    return src2dst, seg, dst_tok
+
+
+def _combine(down_out, src2dst, topk_weight, T, k, out_dtype):
+    """moe/all2all_moe.py:270-278: f32 weighting and sum over k."""
+    H = down_out.shape[1]
+    return (down_out[src2dst.long()].view(T, k, H).float()
+            * topk_weight.float().unsqueeze(-1)).sum(dim=1).to(out_dtype)
+
+
+def moe_layer_w4a16(x, topk_ids, topk_weight, w13_q, w13_scale, w13_zero, w2_q, w2_scale, w2_zero,
+                    out_dtype=torch.bfloat16):
+    """w4a16 layer: bf16 rows are permuted unquantized (moe/group_gemm_kernel.py:81-117); each
+    expert multiplies by its dequantized int4 weights ((q - zero) * scale rounded to bf16, the
+    zero-point extension of fast_dequant/simple_marlin/utils.py:98-136) with f32 accumulation;
+    SwiGLU with the roundings of moe/group_gemm_kernel.py:120-168; f32 combine.
+    w13_q uint8 [E,2I,H] (unpacked nibbles), scales/zeros bf16 [E,2I,H/128]; w2_* likewise."""
+    T, k = topk_ids.shape
+    E = w13_q.shape[0]
+    src2dst, seg, dst_tok = _permuted_rows(x, topk_ids, E)
+    a = x[dst_tok]
+    down = torch.zeros(T * k, x.shape[1], dtype=out_dtype, device=x.device)
+    segl = seg.tolist()
+    for e in range(E):
+        m0, m1 = segl[e], segl[e + 1]
+        if m1 <= m0:
+            continue
+        w13 = w4a16_dequant(w13_q[e], w13_scale[e], w13_zero[e]).float()
+        gu = (a[m0:m1].float() @ w13.t()).to(out_dtype)
+        h = torch.empty(m1 - m0, gu.shape[1] // 2, dtype=out_dtype, device=x.device)
+        silu_and_mul(gu, torch.zeros(m1 - m0, dtype=torch.long), None, 0, 0, h)
+        w2 = w4a16_dequant(w2_q[e], w2_scale[e], w2_zero[e]).float()
+        down[m0:m1] = (h.float() @ w2.t()).to(out_dtype)
+    return _combine(down, src2dst, topk_weight, T, k, out_dtype)
+
+
+def moe_layer_w4a8(x, topk_ids, topk_weight, w13, w2, out_dtype=torch.bfloat16):
+    """w4a8 layer: tokens are quantized to int8 per 1x128 group (quantization/w4a8_kernel.py:145-193)
+    before the permutation; each expert runs w4a8_gemm (:317-448) for gate/up, SwiGLU
+    (moe/group_gemm_kernel.py:120-168), re-quantizes to int8, runs w4a8_gemm for down; f32
+    combine.  w13, w2: per-expert lists of (packed, s, s4, z4) from w4a8_weight_quant."""
+    T, k = topk_ids.shape
+    E = len(w13)
+    src2dst, seg, dst_tok = _permuted_rows(x, topk_ids, E)
+    xq, xs = act_quant_int8(x.contiguous(), rounding="floor_half")
+    a, a_s = xq[dst_tok], xs[dst_tok]
+    down = torch.zeros(T * k, x.shape[1], dtype=out_dtype, device=x.device)
+    segl = seg.tolist()
+    for e in range(E):
+        m0, m1 = segl[e], segl[e + 1]
+        if m1 <= m0:
+            continue
+        gu = w4a8_gemm(a[m0:m1], a_s[m0:m1], *w13[e], out_dtype=out_dtype)
+        h = torch.empty(m1 - m0, gu.shape[1] // 2, dtype=out_dtype, device=x.device)
+        silu_and_mul(gu, torch.zeros(m1 - m0, dtype=torch.long), None, 0, 0, h)
+        hq, hs = act_quant_int8(h, rounding="floor_half")
+        down[m0:m1] = w4a8_gemm(hq, hs, *w2[e], out_dtype=out_dtype)
+    return _combine(down, src2dst, topk_weight, T, k, out_dtype)
+
+
 def rel_fro(a: torch.Tensor, b: torch.Tensor) -> float:
     """Relative Frobenius error ||a-b|| / ||b|| in fp64."""
     a, b = a.double(), b.double()

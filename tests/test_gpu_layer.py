@@ -111,3 +111,61 @@ def test_layer_full_size_properties():
     y_ref = R.moe_layer_fp8(x, idx, w, layer.w13_weight, layer.w13_weight_scale, layer.w2_weight,
                             layer.w2_weight_scale)
     assert R.rel_fro(y1.float(), y_ref.float()) < 1e-2
+
+
+def _seeded_router_and_tokens(shape):
+    from llm_kernels_b200 import workloads as WL
+    W, bias = WL.router_params(shape)
+    b = bias if shape.scoring == "sigmoid" else None
+    x = WL.tokens(shape)
+    idx, w = R.gate_forward(x, W, b, top_k=shape.top_k, n_group=shape.n_group, topk_group=shape.topk_group,
+                            scoring_func=shape.scoring, routed_scaling_factor=shape.scaling)
+    return x, idx, w
+
+
+def test_layer_w4a16_mixtral_shape_reduced():
+    """configs[2] (Mixtral-shape w4a16: 8 experts, softmax top-2, asymmetric int4 g128 with bf16
+    scale/zero) at reduced H/I/T.  Output within relative Frobenius error 3e-3."""
+    from llm_kernels_b200 import workloads as WL
+    from dataclasses import replace
+    dev = torch.device("cuda:0")
+    shape = replace(WL.CONFIG2, tokens=300, hidden=512, inter=768)
+    x, idx, w = _seeded_router_and_tokens(shape)
+    qs = [[], [], [], [], [], []]
+    for e in range(shape.experts):
+        g, u, d = WL.expert_weights_cpu(shape, e)
+        q, s, z = R.w4a16_quantize_asym(torch.cat([g, u], 0))
+        qs[0].append(q); qs[1].append(s); qs[2].append(z)
+        q, s, z = R.w4a16_quantize_asym(d)
+        qs[3].append(q); qs[4].append(s); qs[5].append(z)
+    y_ref = R.moe_layer_w4a16(x, idx, w, *[torch.stack(v) for v in qs])
+    layer = _build_layer(shape, dev)
+    assert torch.equal(layer.w13_scale.cpu(), torch.stack(qs[1]))
+    y = layer.triton_group_gemm_moe_infer(x.to(dev), idx.to(dev), w.to(dev))
+    layer.check_status()
+    err = R.rel_fro(y.cpu().float(), y_ref.float())
+    assert err < 3e-3, err
+    y_full = layer(x.to(dev).view(1, *x.shape))          # through the CUDA router as well
+    assert R.rel_fro(y_full.cpu().view(-1, shape.hidden).float(), y_ref.float()) < 3e-3
+
+
+def test_layer_w4a8_decode_shape_reduced():
+    """configs[4] (decode-regime w4a8: 64 tokens, 256 experts top-8, two-level int4 weights, int8
+    activations) at reduced H/I.  Output within relative Frobenius error 1e-2."""
+    from llm_kernels_b200 import workloads as WL
+    from dataclasses import replace
+    dev = torch.device("cuda:0")
+    shape = replace(WL.CONFIG4, hidden=512, inter=256)
+    x, idx, w = _seeded_router_and_tokens(shape)
+    w13, w2 = [], []
+    for e in range(shape.experts):
+        g, u, d = WL.expert_weights_cpu(shape, e)
+        w13.append(R.w4a8_weight_quant(torch.cat([g, u], 0)))
+        w2.append(R.w4a8_weight_quant(d))
+    y_ref = R.moe_layer_w4a8(x, idx, w, w13, w2)
+    layer = _build_layer(shape, dev)
+    assert torch.equal(layer.w13_qweight.cpu(), torch.stack([a[0] for a in w13]))
+    y = layer.triton_group_gemm_moe_infer(x.to(dev), idx.to(dev), w.to(dev))
+    layer.check_status()
+    err = R.rel_fro(y.cpu().float(), y_ref.float())
+    assert err < 1e-2, err
