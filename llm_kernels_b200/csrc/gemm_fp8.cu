@@ -69,9 +69,14 @@ struct GemmParams {
   int64_t M_total;
   int N, K, num_groups, num_weights, c_dtype, swiglu;
   int32_t* status;
+  // kBf16 only: split the K loop over `ksplits` tiles that write partial products `split_stride`
+  // bytes apart (the caller sums them in a fixed order), and let the activation's K coordinate
+  // wrap every `a_wrap` bytes (K = repeats of the same activation columns against different
+  // weight columns, e.g. a weight split into bf16 hi/mid/lo parts).
+  int ksplits; int64_t split_stride; int a_wrap;
 };
 
-struct Tile { int m0, m_end, expert, nt; };
+struct Tile { int m0, m_end, expert, nt, ks; };
 
 // The activation tile is fetched with the smallest of four boxes (16/32/64/128 rows) that covers
 // the rows the group still has: a ragged group then moves only its own rows through L2 and the
@@ -81,7 +86,8 @@ struct RowMaps { CUtensorMap m[4]; };
 
 __device__ __forceinline__ Tile decode_tile(const SharedTail* sh, const GemmParams& p, int t,
                                             int num_n_tiles) {
-  const int mt = t / num_n_tiles;
+  const int per = num_n_tiles * p.ksplits;
+  const int mt = t / per;
   int lo = 0, hi = p.num_groups;           // last g with pref[g] <= mt
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -91,7 +97,9 @@ __device__ __forceinline__ Tile decode_tile(const SharedTail* sh, const GemmPara
   tl.m0 = sh->seg[lo] + (mt - sh->pref[lo]) * BM;
   tl.m_end = sh->seg[lo + 1];
   tl.expert = p.widx ? static_cast<int>(p.widx[lo]) : lo;
-  tl.nt = t - mt * num_n_tiles;
+  const int rem = t - mt * per;
+  tl.nt = rem / p.ksplits;
+  tl.ks = rem - tl.nt * p.ksplits;
   return tl;
 }
 
@@ -203,7 +211,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
   }
   __syncthreads();
   const uint32_t tmem_base = sh->tmem_base;
-  const int total_tiles = sh->pref[p.num_groups] * num_n_tiles;
+  const int total_tiles = sh->pref[p.num_groups] * num_n_tiles * p.ksplits;
+  const int KBs = (KB + p.ksplits - 1) / p.ksplits;   // K blocks per split
 
   // Register hand-over: the producer/MMA warpgroup keeps 56 registers per thread, the two
   // promotion warpgroups grow to 224 (384 x 168 = 128 x 56 + 256 x 224).
@@ -223,14 +232,14 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         const int sel = rows <= 16 ? 0 : (rows <= 32 ? 1 : (rows <= 64 ? 2 : 3));
         const CUtensorMap* ma = &tmap_a.m[sel];
         const uint32_t bytes = kBBytes + (16u << sel) * BK;
-        for (int kb = 0; kb < KB; ++kb) {
+        for (int kb = tl.ks * KBs, kb1 = min(KB, kb + KBs); kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + size_t(stage) * kStageBytes;
           uint8_t* sb = sa + kABytes;
           ptx::mbar_arrive_expect_tx(&sh->full[stage], bytes);
           armed |= 1u << stage;
           armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-          ptx::tma_load_2d(sa, ma, &sh->full[stage], kb * BK, tl.m0);
+          ptx::tma_load_2d(sa, ma, &sh->full[stage], p.a_wrap ? (kb * BK) % p.a_wrap : kb * BK, tl.m0);
           ptx::tma_load_2d(sb, &tmap_b, &sh->full[stage], kb * BK, brow0);
           ptx::tma_load_2d(sb + kBBytes / 2, &tmap_b, &sh->full[stage], kb * BK, brow1);
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
@@ -256,9 +265,11 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
       int as = 0; uint32_t aphase = 0;
       bool ok = true;
       for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        for (int kb = 0; kb < KB; ++kb) {
+        const int ks = (t % (num_n_tiles * p.ksplits)) % p.ksplits;
+        const int kb0 = ks * KBs, kb1 = min(KB, kb0 + KBs);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&sh->full[stage], phase, abort_flag)) { ok = false; break; }
-          if (kPromote || kb == 0)
+          if (kPromote || kb == kb0)
             if (!ptx::mbar_wait(&sh->tmem_empty[as], aphase ^ 1u, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
           const uint32_t sa = ptx::smem_u32(smem + size_t(stage) * kStageBytes);
@@ -267,10 +278,10 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
           const uint32_t d = tmem_base + static_cast<uint32_t>(as) * BN;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)   // +32 bytes along K = +2 in the >>4 address field
-            umma_kind<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, (k > 0 || (!kPromote && kb > 0)) ? 1u : 0u);
+            umma_kind<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, (k > 0 || (!kPromote && kb > kb0)) ? 1u : 0u);
           ptx::umma_commit(&sh->empty[stage]);      // smem slot reusable once the MMAs retire
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
-          if (kPromote || kb == KB - 1) {
+          if (kPromote || kb == kb1 - 1) {
             ptx::umma_commit(&sh->tmem_full[as]);   // K-block product (kBf16: whole tile) ready
             if (++as == kAccStages) { as = 0; aphase ^= 1u; }
           }
@@ -362,7 +373,7 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         for (int half = 0; half < 2; ++half) {
           const int col0 = tl.nt * BN + half * 128 + hsel * 64;
           if (row_ok && col0 < p.N) {
-            uint8_t* dst = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(row) * p.c_stride;
+            uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + static_cast<int64_t>(row) * p.c_stride;
             if (p.c_dtype == B200MOE_BF16) store_row64(reinterpret_cast<__nv_bfloat16*>(dst) + col0, acc + half * 64);
             else if (p.c_dtype == B200MOE_F16) store_row64(reinterpret_cast<__half*>(dst) + col0, acc + half * 64);
             else store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
@@ -433,7 +444,8 @@ static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParam
   RowMaps ma;
   CUtensorMap mb;
   for (int i = 0; i < 4; ++i)
-    if (int rc = make_tensor_map_u8(&ma.m[i], a, static_cast<uint64_t>(p.M_total), static_cast<uint64_t>(p.K),
+    if (int rc = make_tensor_map_u8(&ma.m[i], a, static_cast<uint64_t>(p.M_total),
+                                    static_cast<uint64_t>(p.a_wrap ? p.a_wrap : p.K),
                                     static_cast<uint64_t>(a_stride), 16u << i)) return rc;
   if (int rc = make_tensor_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K),
                                   static_cast<uint64_t>(p.K), 128)) return rc;
@@ -462,7 +474,7 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
   if (M == 0) return B200MOE_OK;
   const int esz = c_dtype == B200MOE_F32 ? 4 : 2;
   GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
-               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr};
+               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
 }
@@ -498,7 +510,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
-               num_weights, c_dtype, epilogue, status_word};
+               num_weights, c_dtype, epilogue, status_word, 1, 0, 0};
   return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -533,7 +545,7 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
                   B200MOE_BAD_ARG, "grouped_gemm_i8: c row stride");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word};
+               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0};
   return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -556,6 +568,30 @@ extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_byt
   B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0, B200MOE_BAD_ALIGN, "grouped_gemm_bf16: c row stride alignment");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word};
+               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word, 1, 0, 0};
   return launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+}
+
+// ---- router logits on the tensor cores ------------------------------------------------------
+// logits = x . W^T in f32-equivalent precision from bf16 MMAs: x is bf16 already, W (f32) is
+// split offline into three bf16 parts hi + mid + lo (24 mantissa bits), stored side by side as
+// w3 [E, 3H].  The products x*part are exact in f32, the three partial dot products accumulate
+// in the same TMEM accumulator.  The K loop (3H) is split over `ksplits` CTAs per tile whose
+// partial sums land in partials[ks] and are added in index order by b200moe_router_select.
+extern "C" int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_bf16, float* partials,
+                                            int64_t T, int64_t H, int E, int ksplits, void* stream) {
+  B200MOE_REQUIRE(x_bf16 && w3_bf16 && partials, B200MOE_BAD_ARG, "router_logits_bf16x3: null pointer");
+  B200MOE_REQUIRE(T >= 0 && T < (int64_t(1) << 31) && H > 0 && H % 64 == 0 && E >= 1 && E % 128 == 0 && E <= 1024,
+                  B200MOE_BAD_SHAPE, "router_logits_bf16x3: H=%lld must be a multiple of 64 and E=%d of 128", (long long)H, E);
+  const int64_t KB = 3 * H * 2 / 128;
+  B200MOE_REQUIRE(ksplits >= 1 && ksplits <= 16 && (KB + ksplits - 1) / ksplits * (ksplits - 1) < KB, B200MOE_BAD_ARG,
+                  "router_logits_bf16x3: ksplits=%d leaves an empty split for %lld K blocks", ksplits, (long long)KB);
+  B200MOE_REQUIRE(aligned(x_bf16, 16) && aligned(w3_bf16, 16) && aligned(partials, 16), B200MOE_BAD_ALIGN,
+                  "router_logits_bf16x3: alignment");
+  if (T == 0) return B200MOE_OK;
+  GemmParams p{nullptr, 0, nullptr, partials, static_cast<int64_t>(E) * 4, nullptr, 0, nullptr, nullptr, T, E,
+               static_cast<int>(3 * H * 2), 1, 1, B200MOE_F32, 0, nullptr, ksplits, T * static_cast<int64_t>(E) * 4,
+               static_cast<int>(H * 2)};
+  const int64_t tiles = ((T + BM - 1) / BM) * ((E + BN - 1) / BN) * ksplits;
+  return launch_gemm<kBf16>(x_bf16, H * 2, w3_bf16, p, tiles, as_stream(stream));
 }

@@ -75,12 +75,48 @@ class MoEGate(nn.Module):
         w = self.weight if self.weight.dtype == torch.float32 else self.weight.float()
         bias = self.e_score_correction_bias
         bias = bias if bias.dtype == torch.float32 else bias.float()
-        N.check(N.lib().b200moe_router_topk(
-            N.ptr(x), N.dtype_code(x.dtype), N.ptr(w), N.ptr(bias), T, h, self.n_routed_experts,
-            self.top_k, self.n_group, self.topk_group, 0 if self.scoring_func == "sigmoid" else 1,
-            1 if self.norm_topk_prob else 0, float(self.routed_scaling_factor),
-            N.ptr(topk_idx), N.ptr(topk_weight), N.stream()))
+        E = self.n_routed_experts
+        scoring = 0 if self.scoring_func == "sigmoid" else 1
+        if x.dtype == torch.bfloat16 and E % 128 == 0 and h % 64 == 0 and T >= 256:
+            # tensor-core path: logits from bf16 MMAs against the weight split into three bf16 parts
+            w3 = self._split_weight(w)
+            m_tiles = (T + 127) // 128
+            kb = 3 * h // 64
+            ks = max(1, min(8, 148 // m_tiles))
+            while ks > 1 and -(-kb // ks) * (ks - 1) >= kb:
+                ks -= 1
+            part = self._scratch(ks * T * E)
+            N.check(N.lib().b200moe_router_logits_bf16x3(N.ptr(x), N.ptr(w3), N.ptr(part), T, h, E, ks, N.stream()))
+            N.check(N.lib().b200moe_router_select(
+                N.ptr(part), ks, N.ptr(bias), T, E, self.top_k, self.n_group, self.topk_group, scoring,
+                1 if self.norm_topk_prob else 0, float(self.routed_scaling_factor),
+                N.ptr(topk_idx), N.ptr(topk_weight), N.stream()))
+        else:
+            N.check(N.lib().b200moe_router_topk(
+                N.ptr(x), N.dtype_code(x.dtype), N.ptr(w), N.ptr(bias), T, h, E,
+                self.top_k, self.n_group, self.topk_group, scoring,
+                1 if self.norm_topk_prob else 0, float(self.routed_scaling_factor),
+                N.ptr(topk_idx), N.ptr(topk_weight), N.stream()))
         return topk_idx, topk_weight
+
+    def _split_weight(self, w):
+        """[hi | mid | lo] bf16 parts of the f32 router weight, [E, 3H]; rebuilt when the weight changes."""
+        key = (w.data_ptr(), w._version, tuple(w.shape))
+        if getattr(self, "_w3_key", None) != key:
+            hi = w.to(torch.bfloat16)
+            r1 = w - hi.float()
+            mid = r1.to(torch.bfloat16)
+            lo = (r1 - mid.float()).to(torch.bfloat16)
+            self._w3 = torch.cat([hi, mid, lo], dim=1).contiguous()
+            self._w3_key = key
+        return self._w3
+
+    def _scratch(self, n):
+        t = getattr(self, "_partials", None)
+        if t is None or t.numel() < n or t.device != self.weight.device:
+            t = torch.empty(n, dtype=torch.float32, device=self.weight.device)
+            self._partials = t
+        return t
 
 
 class DeepseekV3MoE(nn.Module):

@@ -142,7 +142,10 @@ def test_router_matches_reference_vectors(dev, golden, case):
 @pytest.mark.parametrize("T,H,E,k,ng,tg,scoring,seed", [
     (512, 1024, 8, 2, 1, 1, "softmax", 0),        # configs[0] router
     (300, 4096, 8, 2, 1, 1, "softmax", 2),        # configs[2] router shape
-    (257, 7168, 256, 8, 8, 4, "sigmoid", 3),      # configs[3] router shape
+    (257, 7168, 256, 8, 8, 4, "sigmoid", 3),      # configs[3] router shape (tensor-core path)
+    (4096, 7168, 256, 8, 8, 4, "sigmoid", 13),    # configs[3] router at its full token count
+    (640, 1024, 128, 6, 4, 2, "softmax", 14),     # tensor-core path, E = 128
+    (300, 4096, 8, 2, 1, 1, "softmax", 15),
     (64, 7168, 256, 8, 1, 1, "sigmoid", 4),
     (1, 128, 32, 4, 4, 2, "sigmoid", 5),
     (33, 256, 64, 6, 1, 1, "softmax", 6),
