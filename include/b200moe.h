@@ -191,6 +191,13 @@ B200MOE_API int b200moe_permute_quant_int8(const void* x, int x_dtype, const int
                                void* out_q, int64_t out_q_row_stride_bytes,
                                float* out_s, int64_t out_s_row_stride, int rounding, void* stream);
 
+/* Row gather: dst row i = src row row_map[i] (rows of row_bytes bytes, a multiple of 16;
+ * negative entries skip the row).  Used to bring rows received in (source rank, expert)
+ * order into expert order; the reference does this on the host with numpy
+ * (moe/all2all_moe.py:229-240). */
+B200MOE_API int b200moe_gather_rows(const void* src, void* dst, const int32_t* row_map, int64_t n,
+                        int64_t row_bytes, void* stream);
+
 /* silu_and_mul_triton_kernel / gelu_and_mul_triton_kernel
  * (moe/group_gemm_kernel.py:120-168, 176-235).  gateup [rows, two_I] =
  * [gate | up]; rows whose reorder_topk_ids is outside [start,end] are skipped
@@ -231,6 +238,8 @@ B200MOE_API int b200moe_post_reorder(const void* down_output, int dtype, void* o
  *   [M_total, N/2] with row stride c_row_stride_bytes and c_s f32
  *   [M_total, N/2/128] with row stride c_s_row_stride.  Intermediates are
  *   rounded to bf16 where the reference rounds to its activation dtype.
+ * c_row_map (epilogue 0 only, may be NULL): int32 [M_total]; output row r is stored at row
+ * c_row_map[r], which un-does a row gather in the store instead of in a separate pass.
  * Rows outside every group are not written.  K % 128 == 0, N % 128 == 0
  * (epilogue 1: N % 256 == 0).  status_word (may be NULL): a device int32 that
  * receives B200MOE_DEVICE_TIMEOUT if a bounded wait inside the kernel expires. */
@@ -242,7 +251,13 @@ B200MOE_API int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byt
                              int64_t M_total, int64_t N, int64_t K,
                              int num_groups, int num_weights,
                              const int64_t* seg_indptr, const int64_t* weight_indices,
-                             int epilogue, int32_t* status_word, void* stream);
+                             int epilogue, const int32_t* c_row_map, int32_t* status_word, void* stream);
+
+/* Caps the grid of the persistent tcgen05 GEMM kernels of this process (0 = one CTA per SM,
+ * the default).  A GEMM CTA owns its whole SM, so an NCCL kernel that is meant to overlap the
+ * GEMM only makes progress if some SMs are left free.  No counterpart in the reference (its
+ * Triton grids are sized by the tile count, moe/group_gemm_kernel.py:484-487). */
+B200MOE_API int b200moe_set_gemm_max_ctas(int max_ctas);
 
 /* ===================== int4 weight paths (w4a8, w4a16) ==================== */
 

@@ -44,7 +44,9 @@ SIGNATURES = {
     "b200moe_act_and_mul": (_i, [_p, _i, _p, _i, _i64, _i64, _p, _p, _i, _i, _i, _p]),
     "b200moe_post_reorder": (_i, [_p, _i, _p, _p, _p, _p, _i, _i, _i64, _i, _i64, _p]),
     "b200moe_grouped_gemm_fp8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _p, _i64,
-                                      _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p]),
+                                      _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p]),
+    "b200moe_gather_rows": (_i, [_p, _p, _p, _i64, _i64, _p]),
+    "b200moe_set_gemm_max_ctas": (_i, [_i]),
     "b200moe_w4a8_expand_int8": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "b200moe_w4a16_expand_bf16": (_i, [_p, _p, _p, _p, _i64, _i64, _p]),
     "b200moe_grouped_gemm_i8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i,

@@ -74,6 +74,8 @@ struct GemmParams {
   // wrap every `a_wrap` bytes (K = repeats of the same activation columns against different
   // weight columns, e.g. a weight split into bf16 hi/mid/lo parts).
   int ksplits; int64_t split_stride; int a_wrap;
+  // plain epilogue: output row r is stored at row c_row_map[r] (null = identity)
+  const int32_t* c_row_map;
 };
 
 struct Tile { int m0, m_end, expert, nt, ks; };
@@ -373,7 +375,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         for (int half = 0; half < 2; ++half) {
           const int col0 = tl.nt * BN + half * 128 + hsel * 64;
           if (row_ok && col0 < p.N) {
-            uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + static_cast<int64_t>(row) * p.c_stride;
+            const int64_t orow = p.c_row_map ? p.c_row_map[row] : row;
+            uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
             if (p.c_dtype == B200MOE_BF16) store_row64(reinterpret_cast<__nv_bfloat16*>(dst) + col0, acc + half * 64);
             else if (p.c_dtype == B200MOE_F16) store_row64(reinterpret_cast<__half*>(dst) + col0, acc + half * 64);
             else store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
@@ -436,6 +439,10 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
 }
 
 // ---- host side ---------------------------------------------------------------------------
+// Upper bound on the persistent grid (0 = one CTA per SM).  A GEMM CTA takes a whole SM
+// (registers and shared memory), so a collective that should run concurrently needs SMs left free.
+static int g_max_ctas = 0;
+
 template <int KIND>
 static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParams p, int64_t tiles_hint,
                        cudaStream_t st) {
@@ -451,6 +458,7 @@ static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParam
                                   static_cast<uint64_t>(p.K), 128)) return rc;
   cudaFuncSetAttribute(gemm_block_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
   int grid = sms;
+  if (g_max_ctas > 0 && g_max_ctas < grid) grid = g_max_ctas;
   if (tiles_hint > 0 && tiles_hint < grid) grid = static_cast<int>(tiles_hint);
   gemm_block_kernel<KIND><<<grid, kThreads, kSmemBytes, st>>>(ma, mb, p);
   return check_launch("gemm_block_kernel");
@@ -474,7 +482,7 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
   if (M == 0) return B200MOE_OK;
   const int esz = c_dtype == B200MOE_F32 ? 4 : 2;
   GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
-               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0};
+               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
 }
@@ -485,8 +493,9 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
                                         int64_t c_s_row_stride, int64_t M_total, int64_t N, int64_t K,
                                         int num_groups, int num_weights, const int64_t* seg_indptr,
                                         const int64_t* weight_indices, int epilogue,
-                                        int32_t* status_word, void* stream) {
+                                        const int32_t* c_row_map, int32_t* status_word, void* stream) {
   B200MOE_REQUIRE(a && a_s && b && b_s && c && seg_indptr, B200MOE_BAD_ARG, "grouped_gemm_fp8: null pointer");
+  B200MOE_REQUIRE(c_row_map == nullptr || epilogue == 0, B200MOE_BAD_ARG, "grouped_gemm_fp8: c_row_map needs epilogue 0");
   B200MOE_REQUIRE(epilogue == 0 || epilogue == 1, B200MOE_BAD_ARG, "grouped_gemm_fp8: epilogue %d", epilogue);
   B200MOE_REQUIRE(M_total >= 0 && M_total < (int64_t(1) << 31) && N > 0 && K > 0 && K % 128 == 0 && N % 128 == 0,
                   B200MOE_BAD_SHAPE, "grouped_gemm_fp8: M=%lld N=%lld K=%lld (N and K must be multiples of 128)",
@@ -510,7 +519,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
-               num_weights, c_dtype, epilogue, status_word, 1, 0, 0};
+               num_weights, c_dtype, epilogue, status_word, 1, 0, 0, c_row_map};
   return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -545,7 +554,7 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
                   B200MOE_BAD_ARG, "grouped_gemm_i8: c row stride");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0};
+               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr};
   return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -568,7 +577,7 @@ extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_byt
   B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0, B200MOE_BAD_ALIGN, "grouped_gemm_bf16: c row stride alignment");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word, 1, 0, 0};
+               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word, 1, 0, 0, nullptr};
   return launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -591,7 +600,13 @@ extern "C" int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_b
   if (T == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, partials, static_cast<int64_t>(E) * 4, nullptr, 0, nullptr, nullptr, T, E,
                static_cast<int>(3 * H * 2), 1, 1, B200MOE_F32, 0, nullptr, ksplits, T * static_cast<int64_t>(E) * 4,
-               static_cast<int>(H * 2)};
+               static_cast<int>(H * 2), nullptr};
   const int64_t tiles = ((T + BM - 1) / BM) * ((E + BN - 1) / BN) * ksplits;
   return launch_gemm<kBf16>(x_bf16, H * 2, w3_bf16, p, tiles, as_stream(stream));
+}
+
+extern "C" int b200moe_set_gemm_max_ctas(int max_ctas) {
+  B200MOE_REQUIRE(max_ctas >= 0, B200MOE_BAD_ARG, "set_gemm_max_ctas: %d", max_ctas);
+  g_max_ctas = max_ctas;
+  return B200MOE_OK;
 }

@@ -198,6 +198,19 @@ __global__ void __launch_bounds__(256) post_reorder_kernel(
   }
 }
 
+// dst row i <- src row row_map[i]; rows are row_bytes long (multiple of 16), one CTA per row.
+__global__ void __launch_bounds__(256) gather_rows_kernel(const uint8_t* __restrict__ src,
+                                                          uint8_t* __restrict__ dst,
+                                                          const int32_t* __restrict__ row_map,
+                                                          int64_t row_bytes) {
+  const int64_t i = blockIdx.x;
+  const int64_t s = row_map[i];
+  if (s < 0) return;
+  const uint4* in = reinterpret_cast<const uint4*>(src + s * row_bytes);
+  uint4* out = reinterpret_cast<uint4*>(dst + i * row_bytes);
+  for (int64_t c = threadIdx.x; c < row_bytes / 16; c += blockDim.x) out[c] = in[c];
+}
+
 static int pick_threads(int64_t chunks) {
   int th = 256;
   while (th > 32 && th / 2 >= chunks) th /= 2;
@@ -293,6 +306,18 @@ extern "C" int b200moe_permute_quant_int8(const void* x, int x_dtype, const int3
   DISPATCH_16BIT_OR_F32(x_dtype, LAUNCH_PQ8)
 #undef LAUNCH_PQ8
   return check_launch("permute_quant_int8");
+}
+
+extern "C" int b200moe_gather_rows(const void* src, void* dst, const int32_t* row_map, int64_t n,
+                                   int64_t row_bytes, void* stream) {
+  B200MOE_REQUIRE(n >= 0 && row_bytes > 0 && row_bytes % 16 == 0, B200MOE_BAD_SHAPE,
+                  "gather_rows: row_bytes=%lld must be a positive multiple of 16", (long long)row_bytes);
+  if (n == 0) return B200MOE_OK;
+  B200MOE_REQUIRE(src && dst && row_map, B200MOE_BAD_ARG, "gather_rows: null pointer");
+  B200MOE_REQUIRE(aligned(src, 16) && aligned(dst, 16), B200MOE_BAD_ALIGN, "gather_rows: 16-byte alignment");
+  gather_rows_kernel<<<static_cast<unsigned>(n), pick_threads(row_bytes / 16), 0, as_stream(stream)>>>(
+      static_cast<const uint8_t*>(src), static_cast<uint8_t*>(dst), row_map, row_bytes);
+  return check_launch("gather_rows");
 }
 
 extern "C" int b200moe_act_and_mul(const void* gateup, int dtype, void* down_input, int out_dtype,

@@ -153,6 +153,12 @@ class DeepseekV3MoE(nn.Module):
         assert H % 128 == 0 and I % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
         self.experts_per_rank = E // self.ep_size
         El = self.experts_per_rank
+        # pipeline passes of the expert-parallel exchange (config.ep_passes; 1 = no overlap)
+        want = int(getattr(config, "ep_passes", 1)) if self.ep_size > 1 else 1
+        self.passes = max(p for p in (1, 2, 4, 8) if p <= max(want, 1) and El % p == 0)
+        if self.passes > 1:
+            # leave SMs for the NCCL kernels that run beside the expert GEMMs (config.ep_gemm_ctas)
+            N.check(N.lib().b200moe_set_gemm_max_ctas(int(getattr(config, "ep_gemm_ctas", 0))))
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self._dev = dev
         reg = lambda name, t: self.register_buffer(name, t, persistent=True)
@@ -265,52 +271,98 @@ class DeepseekV3MoE(nn.Module):
         E = cfg.n_routed_experts
         S = T * k
         assert x.dtype == torch.bfloat16, "activations must be bfloat16"
-        reorder_ids, src2dst, seg_indptr = G.run_moe_ep_preproess(topk_ids, E)
+        ep = self.ep_size
+        # With expert parallelism the experts are visited in (pass, owner rank, expert-in-pass)
+        # order so that every pipeline pass is contiguous on both sides of the exchange.
+        ids = topk_ids if ep == 1 else self._expert_order()[topk_ids]
+        reorder_ids, src2dst, seg_indptr = G.run_moe_ep_preproess(ids, E)
         self._mark("route_metadata")
         rec = self._record_bytes(H)
         send = self._buf("send", (S, rec), torch.uint8)
         if self.method == "fp8_block":
-            G.permute_quant_fp8(x, src2dst, topk_ids, 0, E - 1, send[:, :H],
+            G.permute_quant_fp8(x, src2dst, ids, 0, E - 1, send[:, :H],
                                 send[:, H:H + (H // 128) * 4].view(torch.float32))
         elif self.method == "w4a8":
-            G.permute_quant_int8(x, src2dst, topk_ids, 0, E - 1, send[:, :H],
+            G.permute_quant_int8(x, src2dst, ids, 0, E - 1, send[:, :H],
                                  send[:, H:H + (H // 128) * 4].view(torch.float32), rounding="floor_half")
         else:
-            G.pre_reorder_triton_kernel[(T,)](x, send.view(torch.bfloat16), src2dst, topk_ids, None, 0, E - 1, k, H,
+            G.pre_reorder_triton_kernel[(T,)](x, send.view(torch.bfloat16), src2dst, ids, None, 0, E - 1, k, H,
                                               BLOCK_SIZE=512)
         self._mark("permute_quant")
+        ctx = {}
+        run = getattr(self, "_experts_" + self.method)
 
-        if self.ep_size == 1:
-            rows_buf, rows = send, S
-            seg, widx = seg_indptr, None
+        if ep == 1:
+            self.last_recv_rows = S
+            down = self._buf("down", (S, H), torch.bfloat16)
+            self._last = (send, S, seg_indptr, None)
+            if S > 0:
+                run(ctx, send, S, seg_indptr, None, down, (0, S))
         else:
-            # Received rows stay ordered by (source rank, local expert); each such run is one
-            # GEMM group that reaches its expert through weight_indices, so the reference's
-            # host-side re-sort (:229-240) is not needed.
-            plan = ep_comm.plan_exchange(seg_indptr, self.ep_size)
+            P = self.passes
+            plan = ep_comm.plan_exchange_pipelined(seg_indptr, ep, P)
             rows = plan.recv_rows
-            rows_buf = self._buf("recv", (max(rows, 1), rec), torch.uint8)[:rows]
-            ep_comm.dispatch(plan, send, rows_buf)
-            seg, widx = plan.seg_indptr, plan.weight_indices
-            self._mark("dispatch_a2a")
-        self.last_recv_rows = rows
-
-        down = self._buf("down", (rows, H), torch.bfloat16)
-        if rows > 0:
-            getattr(self, "_experts_" + self.method)(rows_buf, rows, seg, widx, down)
-
-        if self.ep_size > 1:
+            self.last_recv_rows = rows
+            recv = self._buf("recv", (max(rows, 1), rec), torch.uint8)[:rows]
+            down_r = self._buf("down", (max(rows, 1), H), torch.bfloat16)[:rows]
             back = self._buf("back", (S, H), torch.bfloat16)
-            down = ep_comm.combine(plan, down, back)
-            self._mark("combine_a2a")
+            self._last = (recv, rows, plan.seg_indptr, plan.weight_indices)
+            main, comm = torch.cuda.current_stream(), self._comm_stream()
+            ready = torch.cuda.Event()
+            ready.record(main)
+            got = [torch.cuda.Event() for _ in range(P)]
+            done = [torch.cuda.Event() for _ in range(P)]
+            with torch.cuda.stream(comm):
+                comm.wait_event(ready)
+                for p in range(P):
+                    ep_comm.dispatch_pass(plan, p, send, recv)
+                    got[p].record(comm)
+            gpp = plan.groups_per_pass
+            merge = self.method == "fp8_block"      # rows of one expert from all sources -> one GEMM group
+            if merge:
+                merged = self._buf("merged", (max(rows, 1), rec), torch.uint8)[:rows]
+                ctx["c_row_map"] = plan.gather_map
+                self._last = (merged, rows, plan.merged_seg, plan.merged_widx)
+            epp = plan.experts_per_pass
+            for p in range(P):
+                main.wait_event(got[p])
+                r0, r1 = plan.recv_off[p], plan.recv_off[p + 1]
+                if r1 > r0 and merge:
+                    G.gather_rows(recv, merged[r0:r1], plan.gather_map[r0:r1])
+                    run(ctx, merged, rows, plan.merged_seg[p * epp:(p + 1) * epp + 1],
+                        plan.merged_widx[p * epp:(p + 1) * epp], down_r, (r0, r1))
+                elif r1 > r0:
+                    run(ctx, recv, rows, plan.seg_indptr[p * gpp:(p + 1) * gpp + 1],
+                        plan.weight_indices[p * gpp:(p + 1) * gpp], down_r, (r0, r1))
+                done[p].record(main)
+                with torch.cuda.stream(comm):
+                    comm.wait_event(done[p])
+                    ep_comm.combine_pass(plan, p, down_r, back)
+                    if p == P - 1:
+                        ready.record(comm)
+            main.wait_event(ready)
+            self._mark("experts_and_exchange")
+            down = back
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
-        G.post_reorder_triton_kernel[(T,)](down, out, src2dst, topk_ids, topk_weight, 0, E - 1, k, H,
+        G.post_reorder_triton_kernel[(T,)](down, out, src2dst, ids, topk_weight, 0, E - 1, k, H,
                                            BLOCK_SIZE=512)
         self._mark("post_reorder")
         return out
 
+    def _expert_order(self):
+        t = self._buffers_cache.get("expert_order")
+        if t is None:
+            t = ep_comm.expert_order(self.config.n_routed_experts, self.ep_size, self.passes, self._dev)
+            self._buffers_cache["expert_order"] = t
+        return t
+
+    def _comm_stream(self):
+        if getattr(self, "_cs", None) is None:
+            self._cs = torch.cuda.Stream(device=self._dev)
+        return self._cs
+
     # ---- expert FFNs over the permuted rows ---------------------------------------------
-    def _experts_fp8_block(self, buf, rows, seg, widx, down):
+    def _experts_fp8_block(self, ctx, buf, rows, seg, widx, down, rng):
         H, I = self.config.hidden_size, self.config.moe_intermediate_size
         a_q, a_s = buf[:, :H], buf[:, H:H + (H // 128) * 4].view(torch.float32)
         h_q = self._buf("h_q", (rows, I), torch.uint8)
@@ -319,40 +371,70 @@ class DeepseekV3MoE(nn.Module):
                            h_q, h_s, epilogue=1, status_word=self._status)
         self._mark("gemm1_swiglu")
         G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
-                           down, None, epilogue=0, status_word=self._status)
+                           down, None, epilogue=0, status_word=self._status, c_row_map=ctx.get("c_row_map"))
         self._mark("gemm2")
 
-    def _experts_w4a16(self, buf, rows, seg, widx, down):
+    def _experts_w4a16(self, ctx, buf, rows, seg, widx, down, rng):
         I = self.config.moe_intermediate_size
         a = buf.view(torch.bfloat16)
-        w13 = w4a16_kernel.expand_bf16(self.w13_qweight, self.w13_scale, self.w13_zero)
-        self._mark("expand_w13")
+        if "w13" not in ctx:      # int4 -> bf16 once per forward, shared by the pipeline passes
+            ctx["w13"] = w4a16_kernel.expand_bf16(self.w13_qweight, self.w13_scale, self.w13_zero)
+            ctx["w2"] = w4a16_kernel.expand_bf16(self.w2_qweight, self.w2_scale, self.w2_zero)
+            self._mark("expand_weights")
         h = self._buf("h_bf16", (rows, I), torch.bfloat16)
-        G.grouped_gemm_bf16(a, w13, seg, widx, h, epilogue=2, status_word=self._status)
+        G.grouped_gemm_bf16(a, ctx["w13"], seg, widx, h, epilogue=2, status_word=self._status)
         self._mark("gemm1_swiglu")
-        del w13
-        w2 = w4a16_kernel.expand_bf16(self.w2_qweight, self.w2_scale, self.w2_zero)
-        self._mark("expand_w2")
-        G.grouped_gemm_bf16(h, w2, seg, widx, down, epilogue=0, status_word=self._status)
+        G.grouped_gemm_bf16(h, ctx["w2"], seg, widx, down, epilogue=0, status_word=self._status)
         self._mark("gemm2")
 
-    def _experts_w4a8(self, buf, rows, seg, widx, down):
+    def _experts_w4a8(self, ctx, buf, rows, seg, widx, down, rng):
         H, I = self.config.hidden_size, self.config.moe_intermediate_size
         a_q, a_s = buf[:, :H].view(torch.int8), buf[:, H:H + (H // 128) * 4].view(torch.float32)
-        w13 = w4a8_kernel.expand_int8(self.w13_qweight, self.w13_s4, self.w13_z4)
-        self._mark("expand_w13")
+        if "w13" not in ctx:      # int4 -> int8 once per forward, shared by the pipeline passes
+            ctx["w13"] = w4a8_kernel.expand_int8(self.w13_qweight, self.w13_s4, self.w13_z4)
+            ctx["w2"] = w4a8_kernel.expand_int8(self.w2_qweight, self.w2_s4, self.w2_z4)
+            self._mark("expand_weights")
         gu = self._buf("gateup", (rows, 2 * I), torch.bfloat16)
-        G.grouped_gemm_i8(a_q, a_s, w13, self.w13_weight_scale, seg, widx, gu, status_word=self._status)
+        G.grouped_gemm_i8(a_q, a_s, ctx["w13"], self.w13_weight_scale, seg, widx, gu, status_word=self._status)
         self._mark("gemm1")
-        del w13
+        r0, r1 = rng                                   # the rows this call's groups cover
         h = self._buf("h_bf16", (rows, I), torch.bfloat16)
-        G.silu_and_mul_triton_kernel[(rows,)](gu, h, 2 * I, None, None, 0, 0, BLOCK_SIZE=512)
-        h_q, h_s = w4a8_kernel.act_quant(h)
+        G.silu_and_mul_triton_kernel[(r1 - r0,)](gu[r0:r1], h[r0:r1], 2 * I, None, None, 0, 0, BLOCK_SIZE=512)
+        h_q = self._buf("h_i8", (rows, I), torch.int8)
+        h_s = self._buf("h_i8_s", (rows, I // 128), torch.float32)
+        q, sc = w4a8_kernel.act_quant(h[r0:r1])
+        h_q[r0:r1].copy_(q)
+        h_s[r0:r1].copy_(sc)
         self._mark("silu_quant")
-        w2 = w4a8_kernel.expand_int8(self.w2_qweight, self.w2_s4, self.w2_z4)
-        self._mark("expand_w2")
-        G.grouped_gemm_i8(h_q, h_s.float(), w2, self.w2_weight_scale, seg, widx, down, status_word=self._status)
+        G.grouped_gemm_i8(h_q, h_s, ctx["w2"], self.w2_weight_scale, seg, widx, down, status_word=self._status)
         self._mark("gemm2")
+
+    @torch.no_grad()
+    def time_expert_gemms(self, iters: int = 10):
+        """Re-launches the two grouped GEMMs of the last forward on its resident inputs (all
+        groups, current stream) and returns their average durations in ms, timed with CUDA
+        events: (gemm1_ms, gemm2_ms, rows).  fp8_block only."""
+        assert self.method == "fp8_block" and getattr(self, "_last", None) is not None
+        buf, rows, seg, widx = self._last
+        H, I = self.config.hidden_size, self.config.moe_intermediate_size
+        a_q, a_s = buf[:, :H], buf[:, H:H + (H // 128) * 4].view(torch.float32)
+        h_q = self._buf("h_q", (rows, I), torch.uint8)
+        h_s = self._buf("h_s", (rows, I // 128), torch.float32)
+        down = self._buf("down", (max(rows, 1), H), torch.bfloat16)[:rows]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        t1 = t2 = 0.0
+        for _ in range(iters):
+            ev[0].record()
+            G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx, h_q, h_s, epilogue=1,
+                               status_word=self._status)
+            ev[1].record()
+            G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx, down, None, epilogue=0,
+                               status_word=self._status)
+            ev[2].record()
+            ev[2].synchronize()
+            t1 += ev[0].elapsed_time(ev[1])
+            t2 += ev[1].elapsed_time(ev[2])
+        return t1 / iters, t2 / iters, rows
 
     def check_status(self):
         """Raises if a kernel of an earlier forward reported a device-side timeout (synchronises)."""

@@ -140,8 +140,18 @@ def permute_quant_int8(x, src2dst, topk_ids, start_expert_id, end_expert_id, out
                                                {"half_away": 0, "floor_half": 1}[rounding], N.stream()))
 
 
+def gather_rows(src, dst, row_map):
+    """dst[i] = src[row_map[i]] for 2-D byte-addressable row buffers (row size a multiple of 16 bytes)."""
+    N.require_cuda(src, dst, row_map)
+    assert src.is_contiguous() and dst.is_contiguous() and row_map.dtype == torch.int32
+    rb = src.shape[1] * src.element_size()
+    assert dst.shape[1] * dst.element_size() == rb
+    N.check(N.lib().b200moe_gather_rows(N.ptr(src), N.ptr(dst), N.ptr(row_map), row_map.numel(), rb, N.stream()))
+    return dst
+
+
 def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, epilogue: int = 0,
-                     status_word=None):
+                     status_word=None, c_row_map=None):
     """tcgen05 grouped blockwise GEMM on already-quantized activations.
     a [M,K] e4m3/uint8 (row-strided view allowed), a_s [M,K/128] f32 (row-strided view allowed),
     b [W,N,K] e4m3, b_s [W,N/128,K/128] f32, seg_indptr int64 [G+1], weight_indices int64 [G] or
@@ -159,7 +169,7 @@ def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, ep
         N.ptr(a), a.stride(0) * a.element_size(), N.ptr(a_s), a_s.stride(0), N.ptr(b), N.ptr(b_s),
         N.ptr(c), c_dtype, c.stride(0) * c.element_size(),
         N.ptr(c_s), 0 if c_s is None else c_s.stride(0), M, Nn, K, G, W,
-        N.ptr(seg_indptr), N.ptr(weight_indices), epilogue, N.ptr(status_word), N.stream()))
+        N.ptr(seg_indptr), N.ptr(weight_indices), epilogue, N.ptr(c_row_map), N.ptr(status_word), N.stream()))
     return c
 
 

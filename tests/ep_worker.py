@@ -24,7 +24,9 @@ def main():
     dist.init_process_group("nccl", device_id=dev)
     shape = replace(WL.CONFIG3, tokens=96 + 32 * rank, hidden=512, inter=256, experts=32, n_group=4,
                     topk_group=2, top_k=4)
-    layer = DeepseekV3MoE(WL.make_config(shape, ep_size=world), device=dev).eval()
+    cfg = WL.make_config(shape, ep_size=world)
+    cfg.ep_passes = int(os.environ.get("EP_PASSES", "1"))
+    layer = DeepseekV3MoE(cfg, device=dev).eval()
     WL.fill_layer_cpu_seeded(layer, shape)
     x = WL.tokens(shape, rank=rank)
     y = layer(x.to(dev).view(1, shape.tokens, -1))

@@ -107,6 +107,37 @@ torch.testing.assert_close(y, want, rtol=1e-5, atol=1e-5)
 # total rows conserved across the job
 tot = torch.tensor([plan.recv_rows, T * k]); dist.all_reduce(tot)
 assert int(tot[0]) == int(tot[1])
+# pipelined plan: experts visited in (pass, owner, expert-in-pass) order, 2 passes
+P = 2
+order = ep_comm.expert_order(E, world, P, "cpu")
+ids_r = order[ids]
+_, s2d, seg = R.run_moe_ep_preproess(ids_r, E)
+send = torch.empty(T * k, H)
+send[s2d.long()] = x.repeat_interleave(k, 0)
+pp = ep_comm.plan_exchange_pipelined(seg, world, P)
+recv = torch.empty(pp.recv_rows, H)
+out = torch.empty_like(recv)
+back = torch.empty(T * k, H)
+Ep = El // P
+sg = pp.seg_indptr.tolist()
+for p in range(P):
+    ep_comm.dispatch_pass(pp, p, send, recv)
+    for gi in range(p * pp.groups_per_pass, (p + 1) * pp.groups_per_pass):
+        le = int(pp.weight_indices[gi])
+        assert p * Ep <= le < (p + 1) * Ep
+        out[sg[gi]:sg[gi + 1]] = recv[sg[gi]:sg[gi + 1]] * (rank * El + le + 1)
+    ep_comm.combine_pass(pp, p, out, back)
+y = (back[s2d.long()].view(T, k, H) * w.unsqueeze(-1)).sum(1)
+torch.testing.assert_close(y, want, rtol=1e-5, atol=1e-5)
+assert sg[-1] == pp.recv_rows == pp.recv_off[-1]
+# merged view: gather_map brings every expert's rows from all sources together
+merged = recv[pp.gather_map.long()]
+ms = pp.merged_seg.tolist()
+out2 = torch.empty_like(recv)
+for gi, le in enumerate(pp.merged_widx.tolist()):
+    out2[pp.gather_map.long()[ms[gi]:ms[gi + 1]]] = merged[ms[gi]:ms[gi + 1]] * (rank * El + le + 1)
+assert ms[-1] == pp.recv_rows and sorted(pp.gather_map.tolist()) == list(range(pp.recv_rows))
+torch.testing.assert_close(out2, out)
 dist.destroy_process_group()
 print("OK", rank)
 '''
