@@ -279,6 +279,9 @@ class DeepseekV3MoE(nn.Module):
         self._mark("route_metadata")
         rec = self._record_bytes(H)
         send = self._buf("send", (S, rec), torch.uint8)
+        # The exchange plan needs only the per-expert counts: its count all-to-all and its one host
+        # read are issued before the permute kernel, which then runs while the host builds the plan.
+        plan = ep_comm.plan_exchange_pipelined(seg_indptr, ep, self.passes) if ep > 1 else None
         if self.method == "fp8_block":
             G.permute_quant_fp8(x, src2dst, ids, 0, E - 1, send[:, :H],
                                 send[:, H:H + (H // 128) * 4].view(torch.float32))
@@ -300,7 +303,6 @@ class DeepseekV3MoE(nn.Module):
                 run(ctx, send, S, seg_indptr, None, down, (0, S))
         else:
             P = self.passes
-            plan = ep_comm.plan_exchange_pipelined(seg_indptr, ep, P)
             rows = plan.recv_rows
             self.last_recv_rows = rows
             recv = self._buf("recv", (max(rows, 1), rec), torch.uint8)[:rows]

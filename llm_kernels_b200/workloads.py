@@ -63,15 +63,28 @@ def make_config(shape: LayerShape, ep_size: int = 1) -> Config:
 
 
 def zipf_bias(shape: LayerShape, gen: torch.Generator) -> torch.Tensor:
-    """e_score_correction_bias that skews expert popularity towards Zipf(s=1.1):
-    expert with popularity rank r (a seeded random permutation of the experts) gets
-    bias = zipf_bias * 0.08 * (log p_r - log p_E) with p_r ~ r^-1.1, so the bias is
-    non-negative (selection scores stay positive, which keeps the reference's
-    masked_fill(0.0) from competing) and the least popular expert gets 0."""
+    """e_score_correction_bias that skews expert popularity towards Zipf(s=1.1).
+
+    The expert with popularity rank r (0 = most popular) gets
+    bias = zipf_bias * 0.08 * (log p_r - log p_last) with p_r ~ (r+1)^-1.1, so the bias is
+    non-negative (selection scores stay positive, which keeps the reference's masked_fill(0.0)
+    from competing) and the least popular expert gets 0.
+
+    Placement: popularity ranks are dealt in serpentine order over 8 blocks of E/8 consecutive experts
+    (the block a rank owns at EP = 8; EP = 2 and 4 own whole blocks), in a seeded random order
+    inside each block.  Per-expert load stays Zipf-skewed (ragged groups, hot experts) while the
+    blocks carry near-equal totals, as an expert placement balanced across ranks would."""
     E = shape.experts
-    ranks = torch.randperm(E, generator=gen).float() + 1.0
-    logp = -1.1 * torch.log(ranks)
-    return (shape.zipf_bias * 0.08 * (logp - logp.min())).float()
+    blocks = 8 if E % 8 == 0 else 1
+    per = E // blocks
+    slot = torch.stack([torch.randperm(per, generator=gen) for _ in range(blocks)])   # [block, position]
+    r = torch.arange(E)
+    blk = torch.where((r // blocks) % 2 == 0, r % blocks, blocks - 1 - r % blocks)
+    expert_of_rank = blk * per + slot[blk, r // blocks]
+    logp = -1.1 * torch.log(r.float() + 1.0)
+    bias = torch.empty(E)
+    bias[expert_of_rank] = shape.zipf_bias * 0.08 * (logp - logp.min())
+    return bias.float()
 
 
 def router_params(shape: LayerShape, device="cpu"):
