@@ -37,9 +37,9 @@ UNIT = "tokens/s"
 NOMINAL_FP8_TFLOPS = 4500.0
 NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE gate/up launch in the ncu capture summarised in
-# profiles/gemm_fp8_block_kernel_cfg3_small.md (32 experts, 4096 rows).  At EP = 1 the full workload has
+# profiles/gemm_block_kernel_fp8_cfg3_small.md (32 experts, 4096 rows).  At EP = 1 the full workload has
 # 8x the experts and 8x the rows, and the traffic (weights once + rows once) grows in proportion.
-NCU_GEMM1_SMALL = {"dram_bytes": 991.911424e6 + 13.596928e6, "experts": 32, "rows": 4096}
+NCU_GEMM1_SMALL = {"dram_bytes": 1027.476e6 + 14.200832e6, "experts": 32, "rows": 4096}
 
 
 def _peaks():
@@ -325,14 +325,14 @@ def run_ours(args):
         tensor_peak = fp8_peak or 2 * peaks["bf16_tflops"]
         if hbm_bound:
             ach = g1_bytes / g1_s / 1e9
-            roof = {"kernel": "gemm_fp8_block_kernel (gate/up + SwiGLU epilogue)", "bound": "hbm", "achieved": ach,
+            roof = {"kernel": "gemm_block_kernel<fp8> (gate/up + SwiGLU epilogue)", "bound": "hbm", "achieved": ach,
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                     "traffic": NCU_GEMM1_SMALL["dram_bytes"] * El / NCU_GEMM1_SMALL["experts"]
                     if rows == NCU_GEMM1_SMALL["rows"] * El // NCU_GEMM1_SMALL["experts"] else None,
                     "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": g1_bytes}
         else:
             ach = g1_flops / g1_s / 1e12
-            roof = {"kernel": "gemm_fp8_block_kernel (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": ach,
+            roof = {"kernel": "gemm_block_kernel<fp8> (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": ach,
                     "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak, "traffic": None,
                     "peak_source": "torch._scaled_mm e4m3 8192^3 measured in this run" if fp8_peak else
                                    f"2 x {peaks['source']} bf16 cuBLAS", "algorithmic_flops": g1_flops}
