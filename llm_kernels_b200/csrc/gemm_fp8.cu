@@ -43,7 +43,7 @@ constexpr int kThreads = (kFirstEpiWarp + kEpiWarps) * 32;
 constexpr uint32_t kABytes = BM * BK;
 constexpr uint32_t kBBytes = BN * BK;
 constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr int kMaxGroups = 2048;
+constexpr int kMaxGroups = 1024;
 constexpr uint32_t kTmemCols = 512;
 
 struct SharedTail {
@@ -55,6 +55,7 @@ struct SharedTail {
   uint32_t tmem_base;
   int abort_flag;
   float amax[2][2][BM];          // [buffer][column half][row]
+  alignas(16) uint8_t out_stage[kEpiWarps][2048];   // per warp: 16 rows x 128 B, 16-byte chunks XOR-swizzled
   int32_t seg[kMaxGroups + 1];   // row offsets of the groups
   int32_t pref[kMaxGroups + 1];  // exclusive prefix of m-tiles per group
 };
@@ -374,12 +375,53 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
           const int col0 = tl.nt * BN + half * 128 + hsel * 64;
-          if (row_ok && col0 < p.N) {
-            const int64_t orow = p.c_row_map ? p.c_row_map[row] : row;
-            uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
-            if (p.c_dtype == B200MOE_BF16) store_row64(reinterpret_cast<__nv_bfloat16*>(dst) + col0, acc + half * 64);
-            else if (p.c_dtype == B200MOE_F16) store_row64(reinterpret_cast<__half*>(dst) + col0, acc + half * 64);
-            else store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
+          if (col0 >= p.N) continue;                       // warp-uniform
+          if (p.c_dtype == B200MOE_F32) {
+            if (row_ok) {
+              const int64_t orow = p.c_row_map ? p.c_row_map[row] : row;
+              uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
+              store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
+            }
+            continue;
+          }
+          // 16-bit outputs: a thread owns 128 contiguous bytes of ITS row, so a direct store touches
+          // 32 cache lines per instruction.  Transpose through shared memory (16 rows at a time,
+          // 16-byte chunks XOR-swizzled by the row) so that 8 lanes write one full 128-byte row.
+          uint4 v[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t w[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float lo = acc[half * 64 + c * 8 + 2 * i], hi = acc[half * 64 + c * 8 + 2 * i + 1];
+              if (p.c_dtype == B200MOE_BF16) { __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi); w[i] = *reinterpret_cast<uint32_t*>(&t); }
+              else { __half2 t = __floats2half2_rn(lo, hi); w[i] = *reinterpret_cast<uint32_t*>(&t); }
+            }
+            v[c] = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+          uint8_t* stg = sh->out_stage[e];
+#pragma unroll
+          for (int part = 0; part < 2; ++part) {
+            if ((lane >> 4) == part) {
+              const int r = lane & 15;
+#pragma unroll
+              for (int c = 0; c < 8; ++c)
+                *reinterpret_cast<uint4*>(stg + r * 128 + ((c ^ (r & 7)) << 4)) = v[c];
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int r = (lane >> 3) + 4 * i;               // row inside this 16-row part
+              const int cc = lane & 7;
+              const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((cc ^ (r & 7)) << 4));
+              const int orow_in = tl.m0 + q * 32 + part * 16 + r;
+              if (orow_in < tl.m_end) {
+                const int64_t orow = p.c_row_map ? p.c_row_map[orow_in] : orow_in;
+                uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
+                *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(col0) * 2 + cc * 16) = val;
+              }
+            }
+            __syncwarp();
           }
         }
       } else if (p.swiglu == 2) {
@@ -416,12 +458,20 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         amax = fmaxf(amax, sh->amax[buf][hsel ^ 1][r_in_tile]);
         if (row_ok) {
           const float scale = __fdiv_rn(amax, 448.f);
+          // h / scale as h * (1/scale) plus one residual correction: equal to the correctly rounded
+          // quotient except in rare last-bit cases, which the e4m3 rounding (3 mantissa bits) absorbs.
+          const float inv = __frcp_rn(scale);
           uint8_t* dst = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(row) * p.c_stride + tl.nt * 128 + hsel * 64;
 #pragma unroll
           for (int j = 0; j < 64; j += 16) {
             float q0[8], q1[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) { q0[i] = __fdiv_rn(acc[j + i], scale); q1[i] = __fdiv_rn(acc[j + 8 + i], scale); }
+            for (int i = 0; i < 8; ++i) {
+              const float a0 = acc[j + i], a1 = acc[j + 8 + i];
+              const float y0 = a0 * inv, y1 = a1 * inv;
+              q0[i] = fmaf(fmaf(-y0, scale, a0), inv, y0);
+              q1[i] = fmaf(fmaf(-y1, scale, a1), inv, y1);
+            }
             const uint2 lo = pack8_e4m3(q0), hi = pack8_e4m3(q1);
             *reinterpret_cast<uint4*>(dst + j) = make_uint4(lo.x, lo.y, hi.x, hi.y);
           }
