@@ -238,7 +238,7 @@ def run_ours(args):
     T, H, k = shape.tokens, shape.hidden, shape.top_k
 
     cfg = WL.make_config(shape, ep_size=world)
-    cfg.ep_passes, cfg.ep_gemm_ctas = args.ep_passes, args.ep_gemm_ctas
+    cfg.ep_passes, cfg.ep_gemm_ctas, cfg.ep_exchange = args.ep_passes, args.ep_gemm_ctas, args.ep_exchange
     layer = DeepseekV3MoE(cfg, device=dev).eval()
     WL.fill_layer_gpu(layer, shape)
     nbatch = 4
@@ -376,6 +376,10 @@ def main():
                     help="cfg3 = the benchmark configuration; small = 1/8 of its experts and tokens (profiler captures)")
     ap.add_argument("--ep-passes", type=int, default=1,
                     help="pipeline passes of the EP exchange (N > 1); 1 = exchange and GEMMs back to back")
+    ap.add_argument("--ep-exchange", default="nccl", choices=["nccl", "push", "fused"],
+                    help="nccl = all_to_all_single; push = peer copies on the copy engines (symmetric memory); "
+                         "fused = records and results stored into the peers' buffers by the permute kernel and "
+                         "the down projection")
     ap.add_argument("--ep-gemm-ctas", type=int, default=0,
                     help="GEMM grid cap while NCCL kernels overlap (N > 1, passes > 1); 0 = all SMs")
     ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens in the CPU baseline sample (0 = skip)")

@@ -240,6 +240,10 @@ B200MOE_API int b200moe_post_reorder(const void* down_output, int dtype, void* o
  *   rounded to bf16 where the reference rounds to its activation dtype.
  * c_row_map (epilogue 0 only, may be NULL): int32 [M_total]; output row r is stored at row
  * c_row_map[r], which un-does a row gather in the store instead of in a separate pass.
+ * c_row_addr (epilogue 0 only, may be NULL, exclusive with c_row_map): int64 [M_total]; output row
+ * r is stored at the byte address c_row_addr[r] (16-byte aligned), which may be a peer mapping of
+ * another GPU's memory: the expert-parallel return trip (the second all_to_all_single of
+ * moe/all2all_moe.py:248-262) then happens in the stores of the down projection.
  * Rows outside every group are not written.  K % 128 == 0, N % 128 == 0
  * (epilogue 1: N % 256 == 0).  status_word (may be NULL): a device int32 that
  * receives B200MOE_DEVICE_TIMEOUT if a bounded wait inside the kernel expires. */
@@ -251,13 +255,21 @@ B200MOE_API int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byt
                              int64_t M_total, int64_t N, int64_t K,
                              int num_groups, int num_weights,
                              const int64_t* seg_indptr, const int64_t* weight_indices,
-                             int epilogue, const int32_t* c_row_map, int32_t* status_word, void* stream);
+                             int epilogue, const int32_t* c_row_map, const int64_t* c_row_addr,
+                             int32_t* status_word, void* stream);
 
 /* Caps the grid of the persistent tcgen05 GEMM kernels of this process (0 = one CTA per SM,
  * the default).  A GEMM CTA owns its whole SM, so an NCCL kernel that is meant to overlap the
  * GEMM only makes progress if some SMs are left free.  No counterpart in the reference (its
  * Triton grids are sized by the tile count, moe/group_gemm_kernel.py:484-487). */
 B200MOE_API int b200moe_set_gemm_max_ctas(int max_ctas);
+
+/* No counterpart in the reference.  Tile shape of the grouped/dense GEMMs above: 0 = one CTA per
+ * 128 x 256 tile, 1 = clusters of two CTAs sharing a 256 x 256 tile (tcgen05 cta_group::2; each
+ * SM then moves 32 KB instead of 48 KB per K block through the crossbar).  Default 0: pairs are
+ * slower for the kinds that promote every K block (the stage hand-over crosses SMs).  Results are
+ * identical in both modes. */
+B200MOE_API int b200moe_set_gemm_pair_mode(int mode);
 
 /* ===================== int4 weight paths (w4a8, w4a16) ==================== */
 
@@ -301,6 +313,61 @@ B200MOE_API int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_by
                               int64_t K, int num_groups, int num_weights,
                               const int64_t* seg_indptr, const int64_t* weight_indices,
                               int epilogue, int32_t* status_word, void* stream);
+
+/* Same with f16 operands (plain epilogue only): the matrix product of the reference's w4a16
+ * `mul` (fast_dequant/simple_marlin/marlin_w4a16_gemm.cpp:23-111) after
+ * b200moe_marlin_expand_f16. */
+B200MOE_API int b200moe_grouped_gemm_f16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
+                             int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                             int64_t K, int num_groups, int num_weights,
+                             const int64_t* seg_indptr, const int64_t* weight_indices,
+                             int32_t* status_word, void* stream);
+
+/* Expands Marlin-order symmetric int4 weights (QuantUtils.pack,
+ * fast_dequant/simple_marlin/utils.py:53-95; dequantization of
+ * marlin_w4a16_gemm.cu:44-64: (q - 8) * scale) to f16 in nn.Linear layout.
+ * packed int32 [K/16, N*2]; scales f16 [K/groupsize, N] (one row when groupsize == -1) in the
+ * permuted order QuantUtils.pack returns; out f16 [N, K].  perm1024 (HOST pointer, int16[1024]):
+ * packed position i of a 1024-element block holds element perm1024[i]; scale_perm_inverse
+ * (HOST pointer, int8[scale_perm_len], 64 grouped / 32 single): packed scale column of original
+ * column n is (n / len) * len + scale_perm_inverse[n % len].  K % 16 == 0, N % 64 == 0. */
+B200MOE_API int b200moe_marlin_expand_f16(const void* packed, const void* scales_f16, void* out_f16,
+                              int64_t K, int64_t N, int64_t groupsize, const int16_t* perm1024,
+                              const int8_t* scale_perm_inverse, int scale_perm_len, void* stream);
+
+/* ============ expert-parallel exchange folded into the kernels ============= */
+/* Replaces the two all_to_all_single calls and the host-side split lists of
+ * moe/all2all_moe.py:131-262 when every rank has peer mappings of every rank's buffers.
+ *
+ * b200moe_ep_plan: counts_all int64 [ep_size, num_experts] (row s = slots rank s routes to each
+ * global expert; expert e lives on rank e / (num_experts / ep_size)), all on the device.
+ * recv_base / back_base: int64 [ep_size] device arrays with the address, as mapped in THIS
+ * process, of each rank's receive buffer ([cap_rows] records of rec_bytes) and return buffer
+ * (rows of back_row_bytes in the owner's sorted slot order).  Outputs, all on the device:
+ *   dst_base  int64 [num_experts]  where my first record for expert e goes (0 = dropped: the
+ *                                  owner's capacity is exceeded; info[1] is set)
+ *   local_seg int64 [E/ep + 1]     group table of my local experts over my receive buffer, rows
+ *                                  ordered (expert, source rank)
+ *   back_addr int64 [cap_rows]     return address of every row I receive (c_row_addr of the
+ *                                  down projection)
+ *   info      int32 [2]            {rows received, overflow flag}
+ * workspace: b200moe_ep_plan_workspace_bytes(ep_size, num_experts) bytes, 8-byte aligned. */
+B200MOE_API int64_t b200moe_ep_plan_workspace_bytes(int ep_size, int num_experts);
+B200MOE_API int b200moe_ep_plan(const int64_t* counts_all, int rank, int ep_size, int num_experts,
+                    int64_t cap_rows, const int64_t* recv_base, int64_t rec_bytes,
+                    const int64_t* back_base, int64_t back_row_bytes, int64_t* dst_base,
+                    int64_t* local_seg, int64_t* back_addr, int32_t* info, void* workspace,
+                    int64_t workspace_bytes, void* stream);
+
+/* permute_quant_fp8 whose records go straight to their owners: the record of a slot routed to
+ * expert e, at position d = src2dst[slot] of my sorted order, is stored at
+ * dst_base[e] + (d - seg_indptr[e]) * rec_bytes: H e4m3 bytes, then H/128 f32 scales at byte H.
+ * The stores may cross NVLink; the kernel ends with a system-scope fence, and the caller orders
+ * the owner's reads behind a barrier across ranks. */
+B200MOE_API int b200moe_permute_quant_fp8_push(const void* x, int x_dtype, const int32_t* src2dst,
+                                   const int64_t* topk_ids, const int64_t* seg_indptr,
+                                   const int64_t* dst_base, int num_experts, int64_t T, int topk,
+                                   int64_t H, int64_t rec_bytes, void* stream);
 
 /* ========================= quantization/bitpack.py ======================== */
 

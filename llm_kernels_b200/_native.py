@@ -17,7 +17,8 @@ LIB_PATH = os.path.join(_HERE, "libb200moe.so")
 
 OK = 0
 F32, F16, BF16, FP8_E4M3, I8 = 0, 1, 2, 3, 4
-_DTYPES = {torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16,
+_DTYPES = {  # torch dtype -> B200MOE_* code
+   torch.float32: F32, torch.float16: F16, torch.bfloat16: BF16,
            torch.float8_e4m3fn: FP8_E4M3, torch.int8: I8}
 
 _p, _i, _i64, _f, _sz = C.c_void_p, C.c_int, C.c_int64, C.c_float, C.c_size_t
@@ -44,14 +45,20 @@ SIGNATURES = {
     "b200moe_act_and_mul": (_i, [_p, _i, _p, _i, _i64, _i64, _p, _p, _i, _i, _i, _p]),
     "b200moe_post_reorder": (_i, [_p, _i, _p, _p, _p, _p, _i, _i, _i64, _i, _i64, _p]),
     "b200moe_grouped_gemm_fp8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _p, _i64,
-                                      _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p]),
+                                      _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p, _p]),
+    "b200moe_ep_plan_workspace_bytes": (_i64, [_i, _i]),
+    "b200moe_ep_plan": (_i, [_p, _i, _i, _i, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _i64, _p]),
+    "b200moe_permute_quant_fp8_push": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i, _i64, _i64, _p]),
     "b200moe_gather_rows": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "b200moe_set_gemm_max_ctas": (_i, [_i]),
+    "b200moe_set_gemm_pair_mode": (_i, [_i]),
     "b200moe_w4a8_expand_int8": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "b200moe_w4a16_expand_bf16": (_i, [_p, _p, _p, _p, _i64, _i64, _p]),
     "b200moe_grouped_gemm_i8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i,
                                      _p, _p, _p, _p]),
     "b200moe_grouped_gemm_bf16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p]),
+    "b200moe_grouped_gemm_f16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p]),
+    "b200moe_marlin_expand_f16": (_i, [_p, _p, _p, _i64, _i64, _i64, _p, _p, _i, _p]),
     "b200moe_pack_bits": (_i, [_p, _p, _i64, _i64, _i, _i, _i, _p]),
     "b200moe_unpack_bits": (_i, [_p, _p, _i64, _i64, _i, _i, _i, _p]),
 }

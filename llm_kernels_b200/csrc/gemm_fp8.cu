@@ -35,7 +35,9 @@
 namespace b200moe {
 
 constexpr int BM = 128, BN = 256, BK = 128;
-constexpr int kStages = 4;
+constexpr int kStages = 4;          // single-CTA tiles: 4 x (16 KB A + 32 KB B)
+constexpr int kPairStages = 6;      // CTA pairs:        6 x (16 KB A + 16 KB B) per CTA
+constexpr int kMaxStages = 6;
 constexpr int kAccStages = 2;
 constexpr int kEpiWarps = 8;
 constexpr int kFirstEpiWarp = 4;
@@ -47,8 +49,8 @@ constexpr int kMaxGroups = 1024;
 constexpr uint32_t kTmemCols = 512;
 
 struct SharedTail {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[kAccStages];
   uint64_t tmem_empty[kAccStages];
   uint64_t amax_bar[2];
@@ -59,6 +61,8 @@ struct SharedTail {
   int32_t seg[kMaxGroups + 1];   // row offsets of the groups
   int32_t pref[kMaxGroups + 1];  // exclusive prefix of m-tiles per group
 };
+constexpr uint32_t kPairStageBytes = kABytes + kBBytes / 2;
+static_assert(kPairStages * kPairStageBytes == kStages * kStageBytes, "both layouts use the same ring size");
 constexpr size_t kSmemBytes = 1024 + size_t(kStages) * kStageBytes + sizeof(SharedTail);
 
 struct GemmParams {
@@ -77,6 +81,10 @@ struct GemmParams {
   int ksplits; int64_t split_stride; int a_wrap;
   // plain epilogue: output row r is stored at row c_row_map[r] (null = identity)
   const int32_t* c_row_map;
+  // plain epilogue: output row r is stored at the byte address c_row_addr[r] (null = unused).
+  // The addresses may lie in another GPU's memory (peer mapping): the rows then cross NVLink as
+  // plain stores straight from the epilogue, and the kernel ends with a system-scope fence.
+  const int64_t* c_row_addr;
 };
 
 struct Tile { int m0, m_end, expert, nt, ks; };
@@ -87,8 +95,9 @@ struct Tile { int m0, m_end, expert, nt, ks; };
 // never stored.
 struct RowMaps { CUtensorMap m[4]; };
 
+// bmt: rows per tile (128, or 256 for a CTA pair); m_off: row offset of this CTA inside the tile.
 __device__ __forceinline__ Tile decode_tile(const SharedTail* sh, const GemmParams& p, int t,
-                                            int num_n_tiles) {
+                                            int num_n_tiles, int bmt = BM, int m_off = 0) {
   const int per = num_n_tiles * p.ksplits;
   const int mt = t / per;
   int lo = 0, hi = p.num_groups;           // last g with pref[g] <= mt
@@ -97,7 +106,7 @@ __device__ __forceinline__ Tile decode_tile(const SharedTail* sh, const GemmPara
     if (sh->pref[mid] <= mt) lo = mid; else hi = mid;
   }
   Tile tl;
-  tl.m0 = sh->seg[lo] + (mt - sh->pref[lo]) * BM;
+  tl.m0 = sh->seg[lo] + (mt - sh->pref[lo]) * bmt + m_off;
   tl.m_end = sh->seg[lo + 1];
   tl.expert = p.widx ? static_cast<int>(p.widx[lo]) : lo;
   const int rem = t - mt * per;
@@ -145,13 +154,13 @@ __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__floa
 //                             as int8 after the int4 -> int8 step of quantization/w4a8_kernel.py:44-101)
 //   kBf16 bf16 x bf16 -> f32, no scales: the whole K loop accumulates in TMEM and the epilogue
 //                             warps read each tile once (w4a16 path after dequantization)
-enum : int { kFp8 = 0, kI8 = 1, kBf16 = 2 };
+enum : int { kFp8 = 0, kI8 = 1, kBf16 = 2, kF16 = 3 };   // kF16: as kBf16 with f16 operands
 
-template <int KIND>
+template <int KIND, int CG>
 __device__ __forceinline__ void umma_kind(uint32_t d, uint64_t a, uint64_t b, uint32_t idesc, uint32_t acc) {
-  if constexpr (KIND == kFp8) ptx::umma_f8f6f4(d, a, b, idesc, acc);
-  else if constexpr (KIND == kI8) ptx::umma_i8(d, a, b, idesc, acc);
-  else ptx::umma_f16(d, a, b, idesc, acc);
+  if constexpr (KIND == kFp8) ptx::umma_f8f6f4<CG>(d, a, b, idesc, acc);
+  else if constexpr (KIND == kI8) ptx::umma_i8<CG>(d, a, b, idesc, acc);
+  else ptx::umma_f16<CG>(d, a, b, idesc, acc);
 }
 
 template <int KIND>
@@ -160,7 +169,15 @@ __device__ __forceinline__ float tmem_value(uint32_t r) {
   else return __uint_as_float(r);
 }
 
-template <int KIND>
+// PAIR: the kernel is launched in clusters of two CTAs that share one 256 x 256 tile
+// (tcgen05 cta_group::2).  CTA r of the pair loads rows [128 r, 128 r + 128) of the activation tile
+// and the r-th 128-row box of the weight tile, so each SM moves 32 KB per K block through the
+// crossbar instead of 48 KB; the even CTA (the leader) issues the MMAs for both, and each CTA
+// promotes and stores the 128 x 256 half that lands in its own tensor memory.  All barriers that
+// order the pair live in the leader: both CTAs' loads count their bytes on the leader's `full`
+// barrier, the leader's commits arrive on `empty` and `tmem_full` of both CTAs, and both CTAs'
+// promotion warps arrive on the leader's `tmem_empty`.
+template <int KIND, bool PAIR>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
                   const __grid_constant__ CUtensorMap tmap_b, const GemmParams p) {
@@ -168,17 +185,26 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   SharedTail* sh = reinterpret_cast<SharedTail*>(smem + size_t(kStages) * kStageBytes);
   volatile int* abort_flag = &sh->abort_flag;
+  constexpr int CG = PAIR ? 2 : 1;
+  constexpr int NS = PAIR ? kPairStages : kStages;                  // ring depth
+  constexpr uint32_t SB = PAIR ? kPairStageBytes : kStageBytes;     // bytes per ring slot in this CTA
+  constexpr int BMT = PAIR ? 2 * BM : BM;                           // rows per tile
+  const uint32_t cta_r = PAIR ? ptx::cluster_ctarank() : 0u;
+  const bool leader = cta_r == 0;
+  const int worker = PAIR ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int nworkers = PAIR ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int m_off = static_cast<int>(cta_r) * BM;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int KB = p.K / BK;                         // p.K is the K extent in BYTES
-  constexpr bool kPromote = KIND != kBf16;
+  constexpr bool kPromote = KIND == kFp8 || KIND == kI8;
   const int NB = p.N / 128;
   const int num_n_tiles = p.swiglu ? (p.N / 2) / 128 : (p.N + BN - 1) / BN;   // swiglu: 0 plain, 1 -> e4m3 + scales, 2 -> bf16
 
   // ---- setup: barriers, TMEM, group table -----------------------------------------
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&sh->full[s], 1); ptx::mbar_init(&sh->empty[s], 1); }
-    for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&sh->tmem_full[s], 1); ptx::mbar_init(&sh->tmem_empty[s], kEpiWarps); }
+    for (int s = 0; s < NS; ++s) { ptx::mbar_init(&sh->full[s], 1); ptx::mbar_init(&sh->empty[s], 1); }
+    for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&sh->tmem_full[s], 1); ptx::mbar_init(&sh->tmem_empty[s], CG * kEpiWarps); }
     ptx::mbar_init(&sh->amax_bar[0], kEpiWarps);
     ptx::mbar_init(&sh->amax_bar[1], kEpiWarps);
     sh->abort_flag = 0;
@@ -189,8 +215,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
     ptx::prefetch_tensormap(&tmap_b);
   }
   if (warp == 1) {
-    ptx::tmem_alloc(&sh->tmem_base, kTmemCols);
-    ptx::tmem_relinquish();
+    ptx::tmem_alloc<CG>(&sh->tmem_base, kTmemCols);
+    ptx::tmem_relinquish<CG>();
   }
   // group row offsets
   for (int g = threadIdx.x; g <= p.num_groups; g += kThreads)
@@ -203,7 +229,7 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
     for (int g0 = 0; g0 < p.num_groups; g0 += 32) {
       const int g = g0 + lane;
       int v = 0;
-      if (g < p.num_groups) { const int m = sh->seg[g + 1] - sh->seg[g]; v = m > 0 ? (m + BM - 1) / BM : 0; }
+      if (g < p.num_groups) { const int m = sh->seg[g + 1] - sh->seg[g]; v = m > 0 ? (m + BMT - 1) / BMT : 0; }
       int incl = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) { const int u = __shfl_up_sync(0xffffffffu, incl, o); if (lane >= o) incl += u; }
@@ -213,6 +239,7 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
     if (lane == 0) sh->pref[p.num_groups] = run;
   }
   __syncthreads();
+  if constexpr (PAIR) ptx::cluster_sync();   // the peer's barriers exist before anything is sent to them
   const uint32_t tmem_base = sh->tmem_base;
   const int total_tiles = sh->pref[p.num_groups] * num_n_tiles * p.ksplits;
   const int KBs = (KB + p.ksplits - 1) / p.ksplits;   // K blocks per split
@@ -227,47 +254,86 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
       int stage = 0; uint32_t phase = 0;
       uint32_t armed = 0, armed_parity = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
-        const Tile tl = decode_tile(sh, p, t, num_n_tiles);
+      auto box_sel = [](int rows) { return rows <= 16 ? 0 : (rows <= 32 ? 1 : (rows <= 64 ? 2 : 3)); };
+      for (int t = worker; ok && t < total_tiles; t += nworkers) {
+        const Tile tl = decode_tile(sh, p, t, num_n_tiles, BMT, m_off);
         const int brow0 = tl.expert * p.N + (p.swiglu ? tl.nt * 128 : tl.nt * BN);
         const int brow1 = p.swiglu ? tl.expert * p.N + p.N / 2 + tl.nt * 128 : brow0 + 128;
-        const int rows = min(BM, tl.m_end - tl.m0);
-        const int sel = rows <= 16 ? 0 : (rows <= 32 ? 1 : (rows <= 64 ? 2 : 3));
+        // a half with no rows left (second CTA of a pair on a group's last tile) still fetches the
+        // smallest box, at or past the group's end: the rows are never stored
+        const int sel = box_sel(min(BM, tl.m_end - tl.m0));
         const CUtensorMap* ma = &tmap_a.m[sel];
-        const uint32_t bytes = kBBytes + (16u << sel) * BK;
+        uint32_t bytes = kBBytes + (16u << sel) * BK;
+        if constexpr (PAIR) bytes += (16u << box_sel(min(BM, tl.m_end - (tl.m0 + BM)))) * BK;   // the peer's box (leader only)
         for (int kb = tl.ks * KBs, kb1 = min(KB, kb + KBs); kb < kb1; ++kb) {
           if (!ptx::mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) { ok = false; break; }
-          uint8_t* sa = smem + size_t(stage) * kStageBytes;
+          uint8_t* sa = smem + size_t(stage) * SB;
           uint8_t* sb = sa + kABytes;
-          ptx::mbar_arrive_expect_tx(&sh->full[stage], bytes);
-          armed |= 1u << stage;
-          armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
-          ptx::tma_load_2d(sa, ma, &sh->full[stage], p.a_wrap ? (kb * BK) % p.a_wrap : kb * BK, tl.m0);
-          ptx::tma_load_2d(sb, &tmap_b, &sh->full[stage], kb * BK, brow0);
-          ptx::tma_load_2d(sb + kBBytes / 2, &tmap_b, &sh->full[stage], kb * BK, brow1);
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+          const int kx = p.a_wrap ? (kb * BK) % p.a_wrap : kb * BK;
+          if constexpr (PAIR) {
+            if (leader) {
+              ptx::mbar_arrive_expect_tx(&sh->full[stage], bytes);
+              armed |= 1u << stage;
+              armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+            }
+            const uint32_t bar = ptx::map_to_cta(ptx::smem_u32(&sh->full[stage]), 0);
+            ptx::tma_load_2d_pair(sa, ma, bar, kx, tl.m0);
+            ptx::tma_load_2d_pair(sb, &tmap_b, bar, kb * BK, leader ? brow0 : brow1);
+          } else {
+            ptx::mbar_arrive_expect_tx(&sh->full[stage], bytes);
+            armed |= 1u << stage;
+            armed_parity = (armed_parity & ~(1u << stage)) | (phase << stage);
+            ptx::tma_load_2d(sa, ma, &sh->full[stage], kx, tl.m0);
+            ptx::tma_load_2d(sb, &tmap_b, &sh->full[stage], kb * BK, brow0);
+            ptx::tma_load_2d(sb + kBBytes / 2, &tmap_b, &sh->full[stage], kb * BK, brow1);
+          }
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
+        }
+      }
+      if constexpr (PAIR) {
+        // Neither CTA of a pair may leave while the other still reads its shared memory or signals
+        // its barriers: wait until every slot this CTA filled has been released by the MMAs.
+        for (int s = 0; ok && s < NS; ++s) {
+          if (!ptx::mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) ok = false;
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
         }
       }
       if (!ok) {
         // leave no bulk copy in flight behind us: wait (bounded) for every armed stage
-        for (int s = 0; s < kStages; ++s) {
+        for (int s = 0; s < NS; ++s) {
           if (!((armed >> s) & 1u)) continue;
           const uint64_t t0 = ptx::global_timer_ns();
           while (!ptx::mbar_try_wait(&sh->full[s], (armed_parity >> s) & 1u) &&
                  ptx::global_timer_ns() - t0 < 20000000ull) {}
         }
+        if (PAIR && !leader) {
+          // this CTA's copies are counted on the leader's barriers; they take microseconds
+          const uint64_t t0 = ptx::global_timer_ns();
+          while (ptx::global_timer_ns() - t0 < 1000000ull) {}
+        }
       }
     }
   } else if (warp == 1) {
     // ================================ MMA issuer ==================================
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       // D f32 (1) / s32 (2); operand formats: e4m3 = 0, signed int8 = 1, bf16 = 1
-      constexpr uint32_t idesc = KIND == kFp8 ? ptx::umma_idesc(1, 0, 0, BM, BN)
-                                 : (KIND == kI8 ? ptx::umma_idesc(2, 1, 1, BM, BN) : ptx::umma_idesc(1, 1, 1, BM, BN));
+      constexpr uint32_t idesc = KIND == kFp8 ? ptx::umma_idesc(1, 0, 0, BMT, BN)
+                                 : (KIND == kI8 ? ptx::umma_idesc(2, 1, 1, BMT, BN)
+                                 : (KIND == kBf16 ? ptx::umma_idesc(1, 1, 1, BMT, BN) : ptx::umma_idesc(1, 0, 0, BMT, BN)));
+      // one arrive per CTA of the pair, on the barrier at the same offset
+      auto commit = [&](uint64_t* bar) {
+        if constexpr (PAIR) {
+          const uint32_t a = ptx::smem_u32(bar);
+          ptx::umma_commit_pair(ptx::map_to_cta(a, 0));
+          ptx::umma_commit_pair(ptx::map_to_cta(a, 1));
+        } else {
+          ptx::umma_commit(bar);
+        }
+      };
       int stage = 0; uint32_t phase = 0;
       int as = 0; uint32_t aphase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      for (int t = worker; ok && t < total_tiles; t += nworkers) {
         const int ks = (t % (num_n_tiles * p.ksplits)) % p.ksplits;
         const int kb0 = ks * KBs, kb1 = min(KB, kb0 + KBs);
         for (int kb = kb0; kb < kb1; ++kb) {
@@ -275,17 +341,17 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
           if (kPromote || kb == kb0)
             if (!ptx::mbar_wait(&sh->tmem_empty[as], aphase ^ 1u, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
-          const uint32_t sa = ptx::smem_u32(smem + size_t(stage) * kStageBytes);
+          const uint32_t sa = ptx::smem_u32(smem + size_t(stage) * SB);
           const uint64_t adesc = ptx::umma_desc_sw128(sa);
           const uint64_t bdesc = ptx::umma_desc_sw128(sa + kABytes);
           const uint32_t d = tmem_base + static_cast<uint32_t>(as) * BN;
 #pragma unroll
           for (int k = 0; k < BK / 32; ++k)   // +32 bytes along K = +2 in the >>4 address field
-            umma_kind<KIND>(d, adesc + 2 * k, bdesc + 2 * k, idesc, (k > 0 || (!kPromote && kb > kb0)) ? 1u : 0u);
-          ptx::umma_commit(&sh->empty[stage]);      // smem slot reusable once the MMAs retire
-          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+            umma_kind<KIND, CG>(d, adesc + 2 * k, bdesc + 2 * k, idesc, (k > 0 || (!kPromote && kb > kb0)) ? 1u : 0u);
+          commit(&sh->empty[stage]);                // smem slot reusable once the MMAs retire
+          if (++stage == NS) { stage = 0; phase ^= 1u; }
           if (kPromote || kb == kb1 - 1) {
-            ptx::umma_commit(&sh->tmem_full[as]);   // K-block product (kBf16: whole tile) ready
+            commit(&sh->tmem_full[as]);             // K-block product (kBf16: whole tile) ready
             if (++as == kAccStages) { as = 0; aphase ^= 1u; }
           }
         }
@@ -321,11 +387,11 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
     };
     Tile tl_next = {};
     ScaleCursor cur_next = {};
-    if (static_cast<int>(blockIdx.x) < total_tiles) {
-      tl_next = decode_tile(sh, p, blockIdx.x, num_n_tiles);
+    if (worker < total_tiles) {
+      tl_next = decode_tile(sh, p, worker, num_n_tiles, BMT, m_off);
       cur_next = open_tile(tl_next);
     }
-    for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+    for (int t = worker; ok && t < total_tiles; t += nworkers, ++it) {
       const Tile tl = tl_next;
       const int row = tl.m0 + r_in_tile;
       const float* as_ptr = cur_next.as_ptr;
@@ -358,7 +424,10 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
         ptx::tc_fence_before_sync();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&sh->tmem_empty[as]);
+        if (lane == 0) {
+          if (PAIR && !leader) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&sh->tmem_empty[as]), 0));
+          else ptx::mbar_arrive(&sh->tmem_empty[as]);
+        }
 #pragma unroll
         for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(tmem_value<KIND>(ra[j]), s1, acc[64 + j]);
 #pragma unroll
@@ -366,8 +435,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         if (++as == kAccStages) { as = 0; aphase ^= 1u; }
       }
       if (!ok) break;
-      if (t + static_cast<int>(gridDim.x) < total_tiles) {
-        tl_next = decode_tile(sh, p, t + gridDim.x, num_n_tiles);
+      if (t + nworkers < total_tiles) {
+        tl_next = decode_tile(sh, p, t + nworkers, num_n_tiles, BMT, m_off);
         cur_next = open_tile(tl_next);
       }
       const bool row_ok = row < tl.m_end;
@@ -379,7 +448,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
           if (p.c_dtype == B200MOE_F32) {
             if (row_ok) {
               const int64_t orow = p.c_row_map ? p.c_row_map[row] : row;
-              uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
+              uint8_t* dst = p.c_row_addr ? reinterpret_cast<uint8_t*>(p.c_row_addr[row])
+                                          : static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
               store_row64(reinterpret_cast<float*>(dst) + col0, acc + half * 64);
             }
             continue;
@@ -417,7 +487,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
               const int orow_in = tl.m0 + q * 32 + part * 16 + r;
               if (orow_in < tl.m_end) {
                 const int64_t orow = p.c_row_map ? p.c_row_map[orow_in] : orow_in;
-                uint8_t* dst = static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
+                uint8_t* dst = p.c_row_addr ? reinterpret_cast<uint8_t*>(p.c_row_addr[orow_in])
+                                            : static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
                 *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(col0) * 2 + cc * 16) = val;
               }
             }
@@ -482,9 +553,11 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
   }
 
   // ---- teardown ----------------------------------------------------------------------
+  if (p.c_row_addr) __threadfence_system();
   ptx::tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) ptx::tmem_dealloc(tmem_base, kTmemCols);
+  if constexpr (PAIR) ptx::cluster_sync();   // both CTAs are done with each other's memory and barriers
+  if (warp == 1) ptx::tmem_dealloc<CG>(tmem_base, kTmemCols);
   if (threadIdx.x == 0 && sh->abort_flag && p.status) *p.status = B200MOE_DEVICE_TIMEOUT;
 }
 
@@ -492,6 +565,31 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
 // Upper bound on the persistent grid (0 = one CTA per SM).  A GEMM CTA takes a whole SM
 // (registers and shared memory), so a collective that should run concurrently needs SMs left free.
 static int g_max_ctas = 0;
+// CTA pairs (256-row tiles): 0 = off (default), 1 = on.  Measured on B200 with 32 groups x 1024
+// rows: bf16/f16 operands gain 5 % from pairs, while the kinds that promote every K block lose
+// 45 % (1.6 -> 0.9 PFLOP/s): the tensor-memory stage hand-over then crosses SMs twice per K block.
+static int g_pair_mode = 0;
+
+template <int KIND, bool PAIR>
+static int launch_gemm_as(const RowMaps& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t st) {
+  cudaFuncSetAttribute(gemm_block_kernel<KIND, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                       static_cast<int>(kSmemBytes));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(static_cast<unsigned>(grid));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = PAIR ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_block_kernel<KIND, PAIR>, ma, mb, p);
+  if (e != cudaSuccess) return fail(B200MOE_LAUNCH_FAILED, "gemm_block_kernel launch: %s", cudaGetErrorString(e));
+  return check_launch("gemm_block_kernel");
+}
 
 template <int KIND>
 static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParams p, int64_t tiles_hint,
@@ -506,12 +604,14 @@ static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParam
                                     static_cast<uint64_t>(a_stride), 16u << i)) return rc;
   if (int rc = make_tensor_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K),
                                   static_cast<uint64_t>(p.K), 128)) return rc;
-  cudaFuncSetAttribute(gemm_block_kernel<KIND>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
   int grid = sms;
   if (g_max_ctas > 0 && g_max_ctas < grid) grid = g_max_ctas;
   if (tiles_hint > 0 && tiles_hint < grid) grid = static_cast<int>(tiles_hint);
-  gemm_block_kernel<KIND><<<grid, kThreads, kSmemBytes, st>>>(ma, mb, p);
-  return check_launch("gemm_block_kernel");
+  // N must cover both halves of a pair's tile; split-K launches stay single.
+  bool pair = g_pair_mode == 1;
+  if (p.ksplits > 1 || grid < 2 || (!p.swiglu && p.N % BN != 0)) pair = false;
+  if (pair) return launch_gemm_as<KIND, true>(ma, mb, p, grid & ~1, st);
+  return launch_gemm_as<KIND, false>(ma, mb, p, grid, st);
 }
 
 }  // namespace b200moe
@@ -532,7 +632,7 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
   if (M == 0) return B200MOE_OK;
   const int esz = c_dtype == B200MOE_F32 ? 4 : 2;
   GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
-               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr};
+               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr, nullptr};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
 }
@@ -543,9 +643,13 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
                                         int64_t c_s_row_stride, int64_t M_total, int64_t N, int64_t K,
                                         int num_groups, int num_weights, const int64_t* seg_indptr,
                                         const int64_t* weight_indices, int epilogue,
-                                        const int32_t* c_row_map, int32_t* status_word, void* stream) {
+                                        const int32_t* c_row_map, const int64_t* c_row_addr,
+                                        int32_t* status_word, void* stream) {
   B200MOE_REQUIRE(a && a_s && b && b_s && c && seg_indptr, B200MOE_BAD_ARG, "grouped_gemm_fp8: null pointer");
-  B200MOE_REQUIRE(c_row_map == nullptr || epilogue == 0, B200MOE_BAD_ARG, "grouped_gemm_fp8: c_row_map needs epilogue 0");
+  B200MOE_REQUIRE((c_row_map == nullptr && c_row_addr == nullptr) || epilogue == 0, B200MOE_BAD_ARG,
+                  "grouped_gemm_fp8: c_row_map / c_row_addr need epilogue 0");
+  B200MOE_REQUIRE(c_row_map == nullptr || c_row_addr == nullptr, B200MOE_BAD_ARG,
+                  "grouped_gemm_fp8: c_row_map and c_row_addr are exclusive");
   B200MOE_REQUIRE(epilogue == 0 || epilogue == 1, B200MOE_BAD_ARG, "grouped_gemm_fp8: epilogue %d", epilogue);
   B200MOE_REQUIRE(M_total >= 0 && M_total < (int64_t(1) << 31) && N > 0 && K > 0 && K % 128 == 0 && N % 128 == 0,
                   B200MOE_BAD_SHAPE, "grouped_gemm_fp8: M=%lld N=%lld K=%lld (N and K must be multiples of 128)",
@@ -569,7 +673,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
-               num_weights, c_dtype, epilogue, status_word, 1, 0, 0, c_row_map};
+               num_weights, c_dtype, epilogue, status_word, 1, 0, 0, c_row_map, c_row_addr};
   return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -604,18 +708,19 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
                   B200MOE_BAD_ARG, "grouped_gemm_i8: c row stride");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr};
+               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr, nullptr};
   return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
-extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
-                                         int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
-                                         int64_t K, int num_groups, int num_weights,
-                                         const int64_t* seg_indptr, const int64_t* weight_indices,
-                                         int epilogue, int32_t* status_word, void* stream) {
+static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
+                              int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                              int64_t K, int num_groups, int num_weights,
+                              const int64_t* seg_indptr, const int64_t* weight_indices,
+                              int epilogue, int32_t* status_word, void* stream) {
   if (int rc = check_grouped_common("grouped_gemm_bf16", a, b, c, seg_indptr, a_row_stride_bytes, 2 * K, M_total, N,
                                     num_groups, num_weights)) return rc;
-  B200MOE_REQUIRE(epilogue == 0 || epilogue == 2, B200MOE_BAD_ARG, "grouped_gemm_bf16: epilogue %d (0 plain, 2 SwiGLU)", epilogue);
+  B200MOE_REQUIRE(epilogue == 0 || (epilogue == 2 && !f16), B200MOE_BAD_ARG,
+                  "grouped_gemm_bf16: epilogue %d (0 plain, 2 SwiGLU with bf16 operands)", epilogue);
   if (epilogue == 2) {
     B200MOE_REQUIRE(N % 256 == 0 && c_dtype == B200MOE_BF16 && c_row_stride_bytes >= N, B200MOE_BAD_ARG,
                     "grouped_gemm_bf16: the SwiGLU epilogue needs N %% 256 == 0 and a bf16 [M, N/2] output");
@@ -627,8 +732,27 @@ extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_byt
   B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0, B200MOE_BAD_ALIGN, "grouped_gemm_bf16: c row stride alignment");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word, 1, 0, 0, nullptr};
-  return launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word, 1, 0, 0, nullptr, nullptr};
+  return f16 ? launch_gemm<kF16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream))
+             : launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+}
+
+extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
+                                         int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                                         int64_t K, int num_groups, int num_weights,
+                                         const int64_t* seg_indptr, const int64_t* weight_indices,
+                                         int epilogue, int32_t* status_word, void* stream) {
+  return grouped_gemm_16bit(false, a, a_row_stride_bytes, b, c, c_dtype, c_row_stride_bytes, M_total, N, K,
+                            num_groups, num_weights, seg_indptr, weight_indices, epilogue, status_word, stream);
+}
+
+extern "C" int b200moe_grouped_gemm_f16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
+                                        int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
+                                        int64_t K, int num_groups, int num_weights,
+                                        const int64_t* seg_indptr, const int64_t* weight_indices,
+                                        int32_t* status_word, void* stream) {
+  return grouped_gemm_16bit(true, a, a_row_stride_bytes, b, c, c_dtype, c_row_stride_bytes, M_total, N, K,
+                            num_groups, num_weights, seg_indptr, weight_indices, 0, status_word, stream);
 }
 
 // ---- router logits on the tensor cores ------------------------------------------------------
@@ -650,9 +774,15 @@ extern "C" int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_b
   if (T == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, partials, static_cast<int64_t>(E) * 4, nullptr, 0, nullptr, nullptr, T, E,
                static_cast<int>(3 * H * 2), 1, 1, B200MOE_F32, 0, nullptr, ksplits, T * static_cast<int64_t>(E) * 4,
-               static_cast<int>(H * 2), nullptr};
+               static_cast<int>(H * 2), nullptr, nullptr};
   const int64_t tiles = ((T + BM - 1) / BM) * ((E + BN - 1) / BN) * ksplits;
   return launch_gemm<kBf16>(x_bf16, H * 2, w3_bf16, p, tiles, as_stream(stream));
+}
+
+extern "C" int b200moe_set_gemm_pair_mode(int mode) {
+  B200MOE_REQUIRE(mode == 0 || mode == 1, B200MOE_BAD_ARG, "set_gemm_pair_mode: %d (0 off, 1 on)", mode);
+  g_pair_mode = mode;
+  return B200MOE_OK;
 }
 
 extern "C" int b200moe_set_gemm_max_ctas(int max_ctas) {

@@ -61,9 +61,64 @@ __global__ void __launch_bounds__(256) w4a16_expand_kernel(const uint32_t* __res
   }
 }
 
+// Marlin-order symmetric int4 (fast_dequant/simple_marlin/utils.py:53-95): packed int32
+// [K/16, N*16/8].  A packed row holds one 16-row k-tile, tiles of 16 x 16 flattened as
+// n_tile*256 + k_in*16 + n_in, permuted in blocks of 1024 by `perm` (packed position i holds
+// element perm[i]) and packed 8 nibbles per word.  Scales f16 [K/g, N] are permuted in blocks of
+// 64 (grouped) or 32 (one group) columns.  One thread expands one word into
+// out[n, k] = (q - 8) * s[k/g, n]  (f16, nn.Linear layout [N, K]).
+__constant__ int16_t c_marlin_perm[1024];
+__constant__ int8_t c_marlin_sinv[64];     // inverse scale permutation (first L entries used)
+
+__global__ void __launch_bounds__(256) marlin_expand_kernel(const uint32_t* __restrict__ packed,
+                                                            const __half* __restrict__ s,
+                                                            __half* __restrict__ out, int64_t K,
+                                                            int64_t N, int64_t groupsize, int L) {
+  const int64_t words_per_row = N * 2;
+  const int64_t total = (K / 16) * words_per_row;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / words_per_row, j = i - r * words_per_row;
+    const uint32_t word = packed[i];
+#pragma unroll
+    for (int f = 0; f < 8; ++f) {
+      const int64_t pcol = j * 8 + f;
+      const int64_t c = (pcol / 1024) * 1024 + c_marlin_perm[pcol % 1024];
+      const int64_t n = (c / 256) * 16 + (c % 16);
+      const int64_t k = r * 16 + (c % 256) / 16;
+      const int64_t g = groupsize > 0 ? k / groupsize : 0;
+      const float sc = __half2float(s[g * N + (n / L) * L + c_marlin_sinv[n % L]]);
+      const int q = static_cast<int>((word >> (4 * f)) & 0xF);
+      out[n * K + k] = __float2half_rn(static_cast<float>(q - 8) * sc);
+    }
+  }
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
+
+extern "C" int b200moe_marlin_expand_f16(const void* packed, const void* scales_f16, void* out_f16,
+                                         int64_t K, int64_t N, int64_t groupsize, const int16_t* perm1024,
+                                         const int8_t* scale_perm_inverse, int scale_perm_len, void* stream) {
+  B200MOE_REQUIRE(packed && scales_f16 && out_f16 && perm1024 && scale_perm_inverse, B200MOE_BAD_ARG,
+                  "marlin_expand_f16: null pointer");
+  B200MOE_REQUIRE(K > 0 && N > 0 && K % 16 == 0 && N % 64 == 0 && (N * 16) % 1024 == 0, B200MOE_BAD_SHAPE,
+                  "marlin_expand_f16: Matrix dimensions not compatible with Marlin kernel requirements (K=%lld N=%lld)",
+                  (long long)K, (long long)N);
+  B200MOE_REQUIRE(groupsize == -1 || (groupsize > 0 && K % groupsize == 0), B200MOE_BAD_SHAPE,
+                  "marlin_expand_f16: K dimension not divisible by groupsize: K=%lld, groupsize=%lld", (long long)K, (long long)groupsize);
+  B200MOE_REQUIRE(scale_perm_len == 64 || scale_perm_len == 32, B200MOE_BAD_ARG, "marlin_expand_f16: scale permutation length %d", scale_perm_len);
+  // the tables are host arrays; they are tiny and re-uploaded per call on the given stream
+  cudaStream_t st = as_stream(stream);
+  cudaMemcpyToSymbolAsync(c_marlin_perm, perm1024, 1024 * sizeof(int16_t), 0, cudaMemcpyHostToDevice, st);
+  cudaMemcpyToSymbolAsync(c_marlin_sinv, scale_perm_inverse, scale_perm_len, 0, cudaMemcpyHostToDevice, st);
+  const int64_t total = (K / 16) * N * 2;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 32));
+  marlin_expand_kernel<<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(packed), static_cast<const __half*>(scales_f16),
+                                             static_cast<__half*>(out_f16), K, N, groupsize, scale_perm_len);
+  return check_launch("marlin_expand_f16");
+}
 
 extern "C" int b200moe_w4a8_expand_int8(const void* packed, const int8_t* s4, const int8_t* z4, void* out,
                                         int64_t W, int64_t N, int64_t K, void* stream) {

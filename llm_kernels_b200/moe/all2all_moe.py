@@ -156,6 +156,17 @@ class DeepseekV3MoE(nn.Module):
         # pipeline passes of the expert-parallel exchange (config.ep_passes; 1 = no overlap)
         want = int(getattr(config, "ep_passes", 1)) if self.ep_size > 1 else 1
         self.passes = max(p for p in (1, 2, 4, 8) if p <= max(want, 1) and El % p == 0)
+        # "nccl": all_to_all_single with split sizes; "push": peer copies on the copy engines;
+        # "fused": records and results stored straight into the peers' buffers by the permute kernel
+        # and the down projection (fp8_block only; no host read, no pipeline passes)
+        self.exchange = getattr(config, "ep_exchange", "nccl") if self.ep_size > 1 else "none"
+        assert self.exchange in ("nccl", "push", "fused", "none")
+        if self.exchange == "fused":
+            assert self.method == "fp8_block", "ep_exchange='fused' is built for quantize_method='fp8_block'"
+            self.passes = 1
+        self._fx = None
+        self.recv_capacity = float(getattr(config, "ep_recv_capacity", 2.0))   # receive rows / (T*k)
+        self._xch = None
         if self.passes > 1:
             # leave SMs for the NCCL kernels that run beside the expert GEMMs (config.ep_gemm_ctas)
             N.check(N.lib().b200moe_set_gemm_max_ctas(int(getattr(config, "ep_gemm_ctas", 0))))
@@ -190,7 +201,7 @@ class DeepseekV3MoE(nn.Module):
             raise NotImplementedError("shared experts are not built yet")
         self._buffers_cache = {}
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
-        self.last_recv_rows = None
+        self._last_recv_rows = None
         # Optional per-stage timing: set to a list and every forward appends
         # (stage name, CUDA event recorded when the stage's launches were queued).
         self.stage_events = None
@@ -281,7 +292,21 @@ class DeepseekV3MoE(nn.Module):
         send = self._buf("send", (S, rec), torch.uint8)
         # The exchange plan needs only the per-expert counts: its count all-to-all and its one host
         # read are issued before the permute kernel, which then runs while the host builds the plan.
-        plan = ep_comm.plan_exchange_pipelined(seg_indptr, ep, self.passes) if ep > 1 else None
+        push = ep > 1 and self.exchange == "push"
+        if ep > 1 and self.exchange == "fused":
+            down = self._run_fused(x, ids, src2dst, seg_indptr, S, H, rec)
+            out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+            G.post_reorder_triton_kernel[(T,)](down, out, src2dst, ids, topk_weight, 0, E - 1, k, H,
+                                               BLOCK_SIZE=512)
+            self._mark("post_reorder")
+            return out
+        if ep == 1:
+            plan = None
+        elif push:
+            pplan = ep_comm.plan_push(seg_indptr, ep, self.passes, self.ep_rank)
+            plan = pplan.base
+        else:
+            plan = ep_comm.plan_exchange_pipelined(seg_indptr, ep, self.passes)
         if self.method == "fp8_block":
             G.permute_quant_fp8(x, src2dst, ids, 0, E - 1, send[:, :H],
                                 send[:, H:H + (H // 128) * 4].view(torch.float32))
@@ -301,6 +326,8 @@ class DeepseekV3MoE(nn.Module):
             self._last = (send, S, seg_indptr, None)
             if S > 0:
                 run(ctx, send, S, seg_indptr, None, down, (0, S))
+        elif push:
+            down = self._run_pushed(ctx, run, pplan, send, S, H, rec)
         else:
             P = self.passes
             rows = plan.recv_rows
@@ -351,6 +378,96 @@ class DeepseekV3MoE(nn.Module):
         self._mark("post_reorder")
         return out
 
+    @property
+    def last_recv_rows(self):
+        """Rows this rank's experts processed in the last forward (synchronises in 'fused' mode)."""
+        v = self._last_recv_rows
+        return int(v.item()) if torch.is_tensor(v) else v
+
+    @last_recv_rows.setter
+    def last_recv_rows(self, v):
+        self._last_recv_rows = v
+
+    def _run_fused(self, x, ids, src2dst, seg_indptr, S, H, rec):
+        """Exchange folded into the permute kernel and the down projection (ep_comm.FusedExchange)."""
+        ep, E = self.ep_size, self.config.n_routed_experts
+        if self._fx is None:
+            smax = torch.tensor([S], dtype=torch.int64, device=self._dev)
+            dist.all_reduce(smax, op=dist.ReduceOp.MAX)      # symmetric allocations: one size on every rank
+            smax = max(int(smax.item()), 1)
+            self._fx = ep_comm.FusedExchange(ep, self.ep_rank, self._dev, int(self.recv_capacity * smax), rec,
+                                             smax, H, E)
+        fx = self._fx
+        assert S <= fx.slots, f"{S} routed slots, peer buffers were sized for {fx.slots} at the first call"
+        fx.gather_counts(seg_indptr)
+        G.ep_plan(fx.counts_all, self.ep_rank, ep, fx.cap_rows, fx.recv_base, rec, fx.back_base, H * 2,
+                  out=(fx.dst_base, fx.local_seg, fx.back_addr, fx.info))
+        self._mark("exchange_plan")
+        G.permute_quant_fp8_push(x, src2dst, ids, seg_indptr, fx.dst_base, rec)
+        fx.barrier()                                         # every rank's records have landed
+        self._mark("permute_quant")
+        self._last_recv_rows = fx.info[0]
+        self._last = (fx.recv, fx.cap_rows, fx.local_seg, None)
+        ctx = {"c_row_addr": fx.back_addr}
+        self._experts_fp8_block(ctx, fx.recv, fx.cap_rows, fx.local_seg, None, fx.back, (0, fx.cap_rows))
+        fx.barrier()                                         # every rank's results have landed
+        self._mark("experts_and_exchange")
+        return fx.back[:S]
+
+    def _run_pushed(self, ctx, run, pplan, send, S, H, rec):
+        """Exchange by peer copies on the copy engines (ep_comm.SymmExchange): every pass's rows are
+        pushed up front, the GEMMs of pass p start when its rows have arrived everywhere, and its
+        results are pushed back while pass p+1 computes."""
+        plan, P, ep = pplan.base, self.passes, self.ep_size
+        rows = plan.recv_rows
+        self.last_recv_rows = rows
+        if self._xch is None:
+            # symmetric allocations must have one size on every rank: size them for the largest batch
+            smax = torch.tensor([S], dtype=torch.int64, device=self._dev)
+            dist.all_reduce(smax, op=dist.ReduceOp.MAX)
+            smax = int(smax.item())
+            self._xch = ep_comm.SymmExchange(ep, self.ep_rank, self._dev, int(self.recv_capacity * smax), rec, smax, H)
+        xch = self._xch
+        assert S <= xch.slots, f"{S} routed slots, peer buffers were sized for {xch.slots} at the first call"
+        assert rows <= xch.cap_rows, f"received {rows} rows, capacity {xch.cap_rows} (raise config.ep_recv_capacity)"
+        recv = xch.recv[:rows]
+        down_r = self._buf("down", (max(rows, 1), H), torch.bfloat16)[:rows]
+        merged = self._buf("merged", (max(rows, 1), rec), torch.uint8)[:rows]
+        merge = self.method == "fp8_block"
+        if merge:
+            ctx["c_row_map"] = plan.gather_map
+            self._last = (merged, rows, plan.merged_seg, plan.merged_widx)
+        else:
+            self._last = (recv, rows, plan.seg_indptr, plan.weight_indices)
+        main = torch.cuda.current_stream()
+        ready = torch.cuda.Event()
+        ready.record(main)
+        got = []
+        for p in range(P):
+            pieces = [(d, xch.peer_recv[d][pplan.dst_off[p][d]:pplan.dst_off[p][d] + plan.in_splits[p][d]],
+                       send[pplan.src_off[p][d]:pplan.src_off[p][d] + plan.in_splits[p][d]]) for d in range(ep)]
+            got.append(xch.push(ready, pieces))
+        gpp, epp = plan.groups_per_pass, plan.experts_per_pass
+        fin = None
+        for p in range(P):
+            main.wait_event(got[p])
+            r0, r1 = plan.recv_off[p], plan.recv_off[p + 1]
+            if r1 > r0 and merge:
+                G.gather_rows(recv, merged[r0:r1], plan.gather_map[r0:r1])
+                run(ctx, merged, rows, plan.merged_seg[p * epp:(p + 1) * epp + 1],
+                    plan.merged_widx[p * epp:(p + 1) * epp], down_r, (r0, r1))
+            elif r1 > r0:
+                run(ctx, recv, rows, plan.seg_indptr[p * gpp:(p + 1) * gpp + 1],
+                    plan.weight_indices[p * gpp:(p + 1) * gpp], down_r, (r0, r1))
+            done = torch.cuda.Event()
+            done.record(main)
+            pieces = [(s_, xch.peer_back[s_][pplan.back_off[p][s_]:pplan.back_off[p][s_] + plan.out_splits[p][s_]],
+                       down_r[pplan.mine_off[p][s_]:pplan.mine_off[p][s_] + plan.out_splits[p][s_]]) for s_ in range(ep)]
+            fin = xch.push(done, pieces)
+        main.wait_event(fin)
+        self._mark("experts_and_exchange")
+        return xch.back[:S]
+
     def _expert_order(self):
         t = self._buffers_cache.get("expert_order")
         if t is None:
@@ -373,7 +490,8 @@ class DeepseekV3MoE(nn.Module):
                            h_q, h_s, epilogue=1, status_word=self._status)
         self._mark("gemm1_swiglu")
         G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
-                           down, None, epilogue=0, status_word=self._status, c_row_map=ctx.get("c_row_map"))
+                           down, None, epilogue=0, status_word=self._status, c_row_map=ctx.get("c_row_map"),
+                           c_row_addr=ctx.get("c_row_addr"))
         self._mark("gemm2")
 
     def _experts_w4a16(self, ctx, buf, rows, seg, widx, down, rng):
@@ -440,6 +558,8 @@ class DeepseekV3MoE(nn.Module):
 
     def check_status(self):
         """Raises if a kernel of an earlier forward reported a device-side timeout (synchronises)."""
+        if self._fx is not None and int(self._fx.info[1].item()):
+            raise N.B200MoeError(1, "a rank received more rows than its peer buffer holds; raise config.ep_recv_capacity")
         s = int(self._status.item())
         if s:
             self._status.zero_()

@@ -142,3 +142,174 @@ def combine_pass(plan: PipelinedPlan, p: int, expert_out: torch.Tensor, back_row
     dist.all_to_all_single(back_rows[plan.send_off[p]:plan.send_off[p + 1]],
                            expert_out[plan.recv_off[p]:plan.recv_off[p + 1]],
                            output_split_sizes=plan.in_splits[p], input_split_sizes=plan.out_splits[p], group=group)
+
+
+# --------------------------------------------------------------------------------------------
+# Copy-engine exchange over peer-mapped (symmetric) memory.  NCCL's all-to-all moves the rows
+# with SM kernels that need a few dozen SMs for bandwidth, while a persistent GEMM CTA owns its
+# SM: the two cannot overlap.  Here every rank PUSHES its rows into the peers' receive buffers
+# with cudaMemcpyAsync peer copies (copy engines, no SMs; one stream per peer), so pass p+1
+# travels while the GEMMs of pass p run.  Arrival is published with a small NCCL all-reduce on
+# the exchange stream (it runs after this rank's copies and completes only when every rank got
+# there), so no hand-written cross-GPU spin-wait is involved.
+# --------------------------------------------------------------------------------------------
+class SymmExchange:
+    """Peer-mapped receive/back buffers and the per-peer copy streams of one layer."""
+
+    def __init__(self, ep_size: int, rank: int, device, cap_rows: int, rec_bytes: int, slots: int, hidden: int,
+                 group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        grp = group if group is not None else dist.group.WORLD
+        self.ep, self.rank, self.cap_rows, self.rec, self.slots = ep_size, rank, cap_rows, rec_bytes, slots
+        self.recv = symm_mem.empty((cap_rows, rec_bytes), dtype=torch.uint8, device=device)
+        self.back = symm_mem.empty((slots, hidden), dtype=torch.bfloat16, device=device)
+        self._hr = symm_mem.rendezvous(self.recv, grp.group_name)
+        self._hb = symm_mem.rendezvous(self.back, grp.group_name)
+        self.peer_recv = [self.recv if r == rank else self._hr.get_buffer(r, (cap_rows, rec_bytes), torch.uint8)
+                          for r in range(ep_size)]
+        self.peer_back = [self.back if r == rank else self._hb.get_buffer(r, (slots, hidden), torch.bfloat16)
+                          for r in range(ep_size)]
+        self.copy_streams = [torch.cuda.Stream(device=device) for _ in range(ep_size)]
+        self.sync_stream = torch.cuda.Stream(device=device)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+        self.group = group
+
+    def _fence(self, after_events):
+        """All ranks' copies recorded in `after_events` (on this rank) and their peers' are done once the
+        all-reduce queued here completes."""
+        st = self.sync_stream
+        for ev in after_events:
+            st.wait_event(ev)
+        with torch.cuda.stream(st):
+            dist.all_reduce(self._flag, group=self.group)
+        ev = torch.cuda.Event()
+        ev.record(st)
+        return ev
+
+    def push(self, ready_event, pieces):
+        """pieces: list of (peer, dst_tensor_slice_on_peer, src_slice).  Queues one peer copy per piece on
+        that peer's stream after `ready_event`; returns the event that marks global completion."""
+        evs = []
+        for peer, dst, src in pieces:
+            if src.numel() == 0:
+                continue
+            st = self.copy_streams[peer]
+            st.wait_event(ready_event)
+            with torch.cuda.stream(st):
+                dst.copy_(src, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(st)
+            evs.append(ev)
+        return self._fence(evs)
+
+
+@dataclass
+class PushPlan:
+    """Host-side offsets of the pushed exchange, from the all-gathered per-expert counts."""
+    base: PipelinedPlan
+    dst_off: List[List[int]]      # [pass][dest]  row in dest's receive buffer where my rows start
+    src_off: List[List[int]]      # [pass][dest]  row in my send buffer where the rows for dest start
+    back_off: List[List[int]]     # [pass][src]   row in src's back buffer where its (pass, me) block starts
+    mine_off: List[List[int]]     # [pass][src]   row in my receive buffer where src's rows start
+
+
+def plan_push(seg_indptr: torch.Tensor, ep_size: int, passes: int, rank: int, group=None) -> PushPlan:
+    """Same ordering and GEMM groups as plan_exchange_pipelined, but every rank learns ALL ranks' counts
+    (one all_gather of E integers per rank, one host read) so that it can compute where its rows land in
+    each peer's buffers."""
+    E = seg_indptr.numel() - 1
+    El = E // ep_size
+    Ep = El // passes
+    dev = seg_indptr.device
+    counts = (seg_indptr[1:] - seg_indptr[:-1]).contiguous()                     # [E] in (pass, dest, j) order
+    allc = torch.empty(ep_size * E, dtype=torch.int64, device=dev)
+    dist.all_gather_into_tensor(allc, counts, group=group)
+    allc5 = allc.view(ep_size, passes, ep_size, Ep)                              # [src, pass, dest, j]
+    recv_counts = allc5[:, :, rank, :].permute(1, 0, 2).contiguous()             # [pass, src, j]
+    tot = allc5.sum(3).cpu()                                                     # [src, pass, dest]  (the host read)
+    tot_l = tot.tolist()
+    in_splits = [[tot_l[rank][p][d] for d in range(ep_size)] for p in range(passes)]
+    out_splits = [[tot_l[s][p][rank] for s in range(ep_size)] for p in range(passes)]
+    send_off, recv_off = [0], [0]
+    for p in range(passes):
+        send_off.append(send_off[-1] + sum(in_splits[p]))
+        recv_off.append(recv_off[-1] + sum(out_splits[p]))
+    # where do things land on the peers
+    def recv_off_of(d, p):      # start of pass p in rank d's receive buffer
+        return sum(tot_l[s][pp][d] for pp in range(p) for s in range(ep_size))
+    def send_off_of(s, p):      # start of pass p in rank s's send buffer
+        return sum(tot_l[s][pp][d] for pp in range(p) for d in range(ep_size))
+    dst_off = [[recv_off_of(d, p) + sum(tot_l[s][p][d] for s in range(rank)) for d in range(ep_size)]
+               for p in range(passes)]
+    src_off = [[send_off[p] + sum(in_splits[p][:d]) for d in range(ep_size)] for p in range(passes)]
+    back_off = [[send_off_of(s, p) + sum(tot_l[s][p][d] for d in range(rank)) for s in range(ep_size)]
+                for p in range(passes)]
+    mine_off = [[recv_off[p] + sum(out_splits[p][:s]) for s in range(ep_size)] for p in range(passes)]
+    # device-side group tables (identical to plan_exchange_pipelined)
+    seg = torch.zeros(passes * ep_size * Ep + 1, dtype=torch.int64, device=dev)
+    seg[1:] = torch.cumsum(recv_counts.reshape(-1), 0)
+    j = torch.arange(Ep, dtype=torch.int64, device=dev)
+    widx = (torch.arange(passes, dtype=torch.int64, device=dev).view(passes, 1, 1) * Ep
+            + j.view(1, 1, Ep)).expand(passes, ep_size, Ep).reshape(-1).contiguous()
+    R = recv_off[-1]
+    c2 = recv_counts.reshape(passes, -1)
+    base_t = torch.tensor(recv_off[:-1], dtype=torch.int64, device=dev).view(passes, 1)
+    src_start = (torch.cumsum(c2, 1) - c2 + base_t).view(passes, ep_size, Ep)
+    ct = recv_counts.transpose(1, 2).contiguous()
+    ct2 = ct.reshape(passes, -1)
+    dst_start = (torch.cumsum(ct2, 1) - ct2 + base_t).view(passes, Ep, ep_size)
+    delta = (src_start.transpose(1, 2) - dst_start).reshape(-1)
+    gather_map = (torch.arange(R, dtype=torch.int64, device=dev)
+                  + torch.repeat_interleave(delta, ct.reshape(-1), output_size=R)).to(torch.int32)
+    mseg = torch.zeros(passes * Ep + 1, dtype=torch.int64, device=dev)
+    mseg[1:] = torch.cumsum(ct.sum(2).reshape(-1), 0)
+    mwidx = torch.arange(passes * Ep, dtype=torch.int64, device=dev)
+    base = PipelinedPlan(passes, in_splits, out_splits, send_off, recv_off, seg, widx, ep_size * Ep,
+                         mseg, mwidx, gather_map, Ep)
+    return PushPlan(base, dst_off, src_off, back_off, mine_off)
+
+
+# --------------------------------------------------------------------------------------------
+# Exchange folded into the kernels.  The permute/quantize kernel stores every record straight into
+# its owner's receive buffer and the down projection stores every output row straight into its
+# source rank's return buffer, both through NVLink peer mappings; the only collective left is the
+# all-gather of the per-expert counts, and nothing is read by the host (see csrc/ep_fused.cu).
+# --------------------------------------------------------------------------------------------
+class FusedExchange:
+    """Peer-mapped receive/return buffers of one layer, their address tables, and the device-side
+    plan outputs.  Construction is collective (symmetric allocation + rendezvous)."""
+
+    def __init__(self, ep_size: int, rank: int, device, cap_rows: int, rec_bytes: int, slots: int, hidden: int,
+                 num_experts: int, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        grp = group if group is not None else dist.group.WORLD
+        self.ep, self.rank, self.cap_rows, self.rec, self.slots = ep_size, rank, cap_rows, rec_bytes, slots
+        self.group = group
+        self.recv = symm_mem.empty((cap_rows, rec_bytes), dtype=torch.uint8, device=device)
+        self.back = symm_mem.empty((slots, hidden), dtype=torch.bfloat16, device=device)
+        self._hr = symm_mem.rendezvous(self.recv, grp.group_name)
+        self._hb = symm_mem.rendezvous(self.back, grp.group_name)
+        self._peers = ([self.recv if r == rank else self._hr.get_buffer(r, (cap_rows, rec_bytes), torch.uint8)
+                        for r in range(ep_size)],
+                       [self.back if r == rank else self._hb.get_buffer(r, (slots, hidden), torch.bfloat16)
+                        for r in range(ep_size)])
+        self.recv_base = torch.tensor([t.data_ptr() for t in self._peers[0]], dtype=torch.int64, device=device)
+        self.back_base = torch.tensor([t.data_ptr() for t in self._peers[1]], dtype=torch.int64, device=device)
+        El = num_experts // ep_size
+        self.counts_all = torch.zeros(ep_size * num_experts, dtype=torch.int64, device=device)
+        self.dst_base = torch.zeros(num_experts, dtype=torch.int64, device=device)
+        self.local_seg = torch.zeros(El + 1, dtype=torch.int64, device=device)
+        self.back_addr = torch.zeros(cap_rows, dtype=torch.int64, device=device)
+        self.info = torch.zeros(2, dtype=torch.int32, device=device)
+        self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def gather_counts(self, seg_indptr: torch.Tensor):
+        counts = (seg_indptr[1:] - seg_indptr[:-1]).contiguous()
+        dist.all_gather_into_tensor(self.counts_all, counts, group=self.group)
+        return self.counts_all
+
+    def barrier(self):
+        """Stream-ordered barrier across the ranks: the all-reduce completes on a rank only after every
+        rank has reached it on its stream, i.e. after the kernels that stored into this rank's buffers
+        (which end with a system-scope fence) have finished."""
+        dist.all_reduce(self._flag, group=self.group)

@@ -151,12 +151,13 @@ def gather_rows(src, dst, row_map):
 
 
 def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, epilogue: int = 0,
-                     status_word=None, c_row_map=None):
+                     status_word=None, c_row_map=None, c_row_addr=None):
     """tcgen05 grouped blockwise GEMM on already-quantized activations.
     a [M,K] e4m3/uint8 (row-strided view allowed), a_s [M,K/128] f32 (row-strided view allowed),
     b [W,N,K] e4m3, b_s [W,N/128,K/128] f32, seg_indptr int64 [G+1], weight_indices int64 [G] or
     None.  epilogue 0: c [M,N] bf16/f16/f32; epilogue 1 (SwiGLU + requant): c [M,N/2] e4m3,
-    c_s [M,N/256] f32."""
+    c_s [M,N/256] f32.  c_row_map int32 [M] / c_row_addr int64 [M] (epilogue 0): row r is stored
+    at row c_row_map[r] of c / at byte address c_row_addr[r] (possibly on another GPU)."""
     N.require_cuda(a, a_s, b, b_s, c)
     assert b.is_contiguous() and b_s.is_contiguous() and a.stride(1) == 1 and a_s.stride(1) == 1
     assert b_s.dtype == torch.float32 and a_s.dtype == torch.float32
@@ -169,8 +170,42 @@ def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, ep
         N.ptr(a), a.stride(0) * a.element_size(), N.ptr(a_s), a_s.stride(0), N.ptr(b), N.ptr(b_s),
         N.ptr(c), c_dtype, c.stride(0) * c.element_size(),
         N.ptr(c_s), 0 if c_s is None else c_s.stride(0), M, Nn, K, G, W,
-        N.ptr(seg_indptr), N.ptr(weight_indices), epilogue, N.ptr(c_row_map), N.ptr(status_word), N.stream()))
+        N.ptr(seg_indptr), N.ptr(weight_indices), epilogue, N.ptr(c_row_map), N.ptr(c_row_addr),
+        N.ptr(status_word), N.stream()))
     return c
+
+
+def ep_plan(counts_all, rank, ep_size, cap_rows, recv_base, rec_bytes, back_base, back_row_bytes, out=None):
+    """Device-side plan of the exchange that is folded into the permute and down-projection kernels
+    (replaces the host-side split lists of moe/all2all_moe.py:150-200).  counts_all int64
+    [ep_size, E]; recv_base / back_base int64 [ep_size] peer-mapped buffer addresses.
+    Returns (dst_base [E], local_seg [E/ep+1], back_addr [cap_rows], info int32 [2])."""
+    N.require_cuda(counts_all, recv_base, back_base)
+    assert counts_all.dtype == torch.int64 and counts_all.is_contiguous()
+    E = counts_all.numel() // ep_size
+    dev = counts_all.device
+    if out is None:
+        out = (torch.empty(E, dtype=torch.int64, device=dev), torch.empty(E // ep_size + 1, dtype=torch.int64, device=dev),
+               torch.empty(cap_rows, dtype=torch.int64, device=dev), torch.empty(2, dtype=torch.int32, device=dev))
+    dst_base, local_seg, back_addr, info = out
+    need = N.lib().b200moe_ep_plan_workspace_bytes(ep_size, E)
+    assert need > 0, "num_experts must be a multiple of ep_size"
+    ws = _workspace(dev, need)
+    N.check(N.lib().b200moe_ep_plan(N.ptr(counts_all), rank, ep_size, E, cap_rows, N.ptr(recv_base), rec_bytes,
+                                    N.ptr(back_base), back_row_bytes, N.ptr(dst_base), N.ptr(local_seg),
+                                    N.ptr(back_addr), N.ptr(info), N.ptr(ws), ws.numel(), N.stream()))
+    return out
+
+
+def permute_quant_fp8_push(x, src2dst, topk_ids, seg_indptr, dst_base, rec_bytes):
+    """permute_quant_fp8 storing every record at its owner: record of expert e at sorted position d
+    -> dst_base[e] + (d - seg_indptr[e]) * rec_bytes (payload, then f32 scales at byte H)."""
+    N.require_cuda(x, src2dst, topk_ids, seg_indptr, dst_base)
+    T, H = x.shape
+    assert x.is_contiguous() and topk_ids.dtype == torch.int64 and dst_base.dtype == torch.int64
+    N.check(N.lib().b200moe_permute_quant_fp8_push(N.ptr(x), N.dtype_code(x.dtype), N.ptr(src2dst), N.ptr(topk_ids),
+                                                   N.ptr(seg_indptr), N.ptr(dst_base), dst_base.numel(), T,
+                                                   topk_ids.shape[1], H, rec_bytes, N.stream()))
 
 
 def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=None):
@@ -190,14 +225,21 @@ def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=N
 
 
 def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, status_word=None):
-    """tcgen05 grouped bf16 GEMM (reference: the scale-free branch of grouped_gemm_triton, :410-412).
-    epilogue 0: c [M,N]; epilogue 2: SwiGLU fused, c bf16 [M,N/2]."""
+    """tcgen05 grouped bf16 or f16 GEMM (reference: the scale-free branch of grouped_gemm_triton,
+    :410-412).  epilogue 0: c [M,N]; epilogue 2 (bf16 operands only): SwiGLU fused, c bf16 [M,N/2]."""
     N.require_cuda(a, b, c)
-    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)
     assert b.is_contiguous() and a.stride(1) == 1
     M, K = a.shape
     W, Nn, Kb = b.shape
     assert Kb == K
+    if a.dtype == torch.float16:
+        assert epilogue == 0, "the fused SwiGLU epilogue takes bf16 operands"
+        N.check(N.lib().b200moe_grouped_gemm_f16(
+            N.ptr(a), a.stride(0) * 2, N.ptr(b), N.ptr(c), N.dtype_code(c.dtype), c.stride(0) * c.element_size(),
+            M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices),
+            N.ptr(status_word), N.stream()))
+        return c
     N.check(N.lib().b200moe_grouped_gemm_bf16(
         N.ptr(a), a.stride(0) * 2, N.ptr(b), N.ptr(c), N.dtype_code(c.dtype), c.stride(0) * c.element_size(),
         M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices), epilogue,
@@ -217,8 +259,8 @@ def grouped_gemm_triton(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, batch
     assert weight_column_major == True  # noqa: E712  (same assert as the reference)
     assert seg_indptr is not None
     if block_shape is None:
-        # scale-free branch (:410-412): bf16 operands, f32 accumulation
-        assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "the unquantized branch takes bfloat16"
+        # scale-free branch (:410-412): f16 or bf16 operands, f32 accumulation
+        assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16), "the unquantized branch takes f16 or bf16"
         seg = seg_indptr if seg_indptr.is_contiguous() else seg_indptr.contiguous()
         return grouped_gemm_bf16(a, b, seg[: batch_size + 1], weight_indices, c, epilogue=0)
     assert list(block_shape) == [128, 128], "only block_shape=[128,128] is supported"

@@ -26,10 +26,12 @@ def main():
                     topk_group=2, top_k=4)
     cfg = WL.make_config(shape, ep_size=world)
     cfg.ep_passes = int(os.environ.get("EP_PASSES", "1"))
+    cfg.ep_exchange = os.environ.get("EP_EXCHANGE", "nccl")
     layer = DeepseekV3MoE(cfg, device=dev).eval()
     WL.fill_layer_cpu_seeded(layer, shape)
     x = WL.tokens(shape, rank=rank)
     y = layer(x.to(dev).view(1, shape.tokens, -1))
+    y = layer(x.to(dev).view(1, shape.tokens, -1))      # twice: buffers and peer mappings are re-used
     layer.check_status()
     torch.cuda.synchronize()
 

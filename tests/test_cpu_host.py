@@ -138,6 +138,19 @@ for gi, le in enumerate(pp.merged_widx.tolist()):
     out2[pp.gather_map.long()[ms[gi]:ms[gi + 1]]] = merged[ms[gi]:ms[gi + 1]] * (rank * El + le + 1)
 assert ms[-1] == pp.recv_rows and sorted(pp.gather_map.tolist()) == list(range(pp.recv_rows))
 torch.testing.assert_close(out2, out)
+# pushed-exchange plan: offsets must describe the same layout as the all-to-all plan
+pl = ep_comm.plan_push(seg, world, P, rank)
+assert pl.base.in_splits == pp.in_splits and pl.base.out_splits == pp.out_splits
+assert torch.equal(pl.base.gather_map, pp.gather_map) and torch.equal(pl.base.merged_seg, pp.merged_seg)
+# gather every rank's view of the offsets and cross-check: what I think I write at peer d must be
+# where d expects rows from me, and the back offsets must mirror the peers' send offsets
+mine = torch.tensor([pl.dst_off, pl.src_off, pl.back_off, pl.mine_off])          # [4, P, world]
+allv = [torch.empty_like(mine) for _ in range(world)]
+dist.all_gather(allv, mine)
+for p in range(P):
+    for d in range(world):
+        assert pl.dst_off[p][d] == int(allv[d][3][p][rank]), "dispatch offset mismatch"
+        assert pl.back_off[p][d] == int(allv[d][1][p][rank]), "combine offset mismatch"
 dist.destroy_process_group()
 print("OK", rank)
 '''
@@ -155,3 +168,17 @@ def test_ep_exchange_world_size_2_gloo(tmp_path):
     for p in procs:
         out, _ = p.communicate(timeout=180)
         assert p.returncode == 0, out
+
+
+def test_marlin_quantutils_match_reference_vectors(golden):
+    """fast_dequant/simple_marlin/utils.py:53-136 on CPU tensors: bit-exact against the reference's output."""
+    import numpy as np
+    from llm_kernels_b200.fast_dequant.simple_marlin.utils import QuantUtils
+    for tag, gs in (("marlin_g128", 128), ("marlin_g-1", -1)):
+        c = golden.case(tag)
+        f = lambda k, dt: torch.from_numpy(np.ascontiguousarray(c[k])).to(dt)
+        ref, q, sc = QuantUtils.fake_quantize(f("w", torch.float16), gs)
+        assert torch.equal(ref, f("ref", torch.float16)) and torch.equal(q, f("q", torch.int32))
+        assert torch.equal(sc, f("scale", torch.float16))
+        pk, ps = QuantUtils.pack(q, sc, gs)
+        assert torch.equal(pk, f("packed", torch.int32)) and torch.equal(ps, f("packed_scale", torch.float16))
