@@ -211,6 +211,7 @@ extern "C" int b200moe_permute_quant_fp8_push(const void* x, int x_dtype, const 
                                               const int64_t* topk_ids, const int64_t* seg_indptr,
                                               const int64_t* dst_base, int num_experts, int64_t T, int topk,
                                               int64_t H, int64_t rec_bytes, void* stream) {
+  if (T == 0) return B200MOE_OK;      // an empty batch has no buffers to check
   B200MOE_REQUIRE(x && src2dst && topk_ids && seg_indptr && dst_base, B200MOE_BAD_ARG, "permute_quant_fp8_push: null pointer");
   B200MOE_REQUIRE(T >= 0 && H > 0 && H % 128 == 0, B200MOE_BAD_SHAPE,
                   "permute_quant_fp8_push: hidden_size=%lld must be divisible by block_size (block_size=128)", (long long)H);

@@ -259,6 +259,7 @@ extern "C" int b200moe_permute_quant_fp8(const void* x, int x_dtype, const int32
                                          int end_expert_id, int64_t T, int topk, int64_t H,
                                          void* out_q, int64_t out_q_row_stride_bytes,
                                          float* out_s, int64_t out_s_row_stride, void* stream) {
+  if (T == 0) return B200MOE_OK;      // an empty batch has no buffers to check
   B200MOE_REQUIRE(x && out_q && out_s && src2dst && topk_ids, B200MOE_BAD_ARG, "permute_quant_fp8: null pointer");
   B200MOE_REQUIRE(T >= 0 && H > 0 && H % 128 == 0, B200MOE_BAD_SHAPE,
                   "permute_quant_fp8: hidden_size=%lld must be divisible by block_size (block_size=128)", (long long)H);
