@@ -343,7 +343,10 @@ def run_ours(args):
             "clocks": clocks,
             "e2e": {"value": e2e_tokens_per_s, "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
                     "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e / args.steps},
-            "gpu_launches": (7 + 2 * layer.passes) * args.steps,
+            # this library's kernels per step: router GEMM + selection, 3 of the counting sort, permute,
+            # un-permute (7); then 2 grouped GEMMs per pass (+ 1 row gather per pass behind the NCCL and
+            # copy-engine exchanges), or 2 plan kernels + 2 grouped GEMMs for the fused exchange
+            "gpu_launches": (7 + (4 if layer.exchange == "fused" else (2 if world == 1 else 3) * layer.passes)) * args.steps,
             "roofline": roof,
             "tokens_per_s_per_gpu": tokens_per_s / world,
             "stages_ms": stages, "rows_rank0": rows,
@@ -376,8 +379,8 @@ def main():
                     help="cfg3 = the benchmark configuration; small = 1/8 of its experts and tokens (profiler captures)")
     ap.add_argument("--ep-passes", type=int, default=1,
                     help="pipeline passes of the EP exchange (N > 1); 1 = exchange and GEMMs back to back")
-    ap.add_argument("--ep-exchange", default="nccl", choices=["nccl", "push", "fused"],
-                    help="nccl = all_to_all_single; push = peer copies on the copy engines (symmetric memory); "
+    ap.add_argument("--ep-exchange", default="auto", choices=["auto", "nccl", "push", "fused"],
+                    help="auto = fused; nccl = all_to_all_single; push = peer copies on the copy engines (symmetric memory); "
                          "fused = records and results stored into the peers' buffers by the permute kernel and "
                          "the down projection")
     ap.add_argument("--ep-gemm-ctas", type=int, default=0,

@@ -169,6 +169,20 @@ __device__ __forceinline__ float tmem_value(uint32_t r) {
   else return __uint_as_float(r);
 }
 
+// acc[0..32) += value(r[0..32)) * s.  The promotion is bound by FMA issue slots (8 warps x 128
+// accumulators per K block), so f32 products go through the packed two-wide FMA.
+template <int KIND>
+__device__ __forceinline__ void promote32(float* acc, const uint32_t (&r)[32], float s) {
+  if constexpr (KIND == kI8) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) acc[j] = fmaf(tmem_value<KIND>(r[j]), s, acc[j]);
+  } else {
+    const uint64_t s2 = ptx::pack_f32x2(s, s);
+#pragma unroll
+    for (int j = 0; j < 32; j += 2) ptx::ffma2(acc[j], acc[j + 1], r[j], r[j + 1], s2);
+  }
+}
+
 // PAIR: the kernel is launched in clusters of two CTAs that share one 256 x 256 tile
 // (tcgen05 cta_group::2).  CTA r of the pair loads rows [128 r, 128 r + 128) of the activation tile
 // and the r-th 128-row box of the weight tile, so each SM moves 32 KB per K block through the
@@ -402,37 +416,49 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
       const int KBp = kPromote ? KB : 1;              // TMEM read-backs per tile
+      // Per K block: two batches of two 32-column loads.  The second batch is in flight during the
+      // FMAs of the first; the first batch of the NEXT K block is issued before the last 64 FMAs of
+      // this one whenever its product is already there, so those FMAs hide its latency too.
+      uint32_t ra[32], rb[32];
+      bool issued = false;                            // first batch of this K block already in flight
       for (int kb = 0; kb < KBp; ++kb) {
         const float s0 = sa_n * b0_n, s1 = sa_n * b1_n;
         if (kPromote && kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
-        // warp-uniform outcome: the TMEM loads below need the whole warp converged
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag))) { ok = false; break; }
-        ptx::tc_fence_after_sync();
         const uint32_t tcol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
-        // Two 32-column loads in flight at any time; the stage goes back to the MMA warp as
-        // soon as its last load has landed, before the last FMAs.
-        uint32_t ra[32], rb[32];
-        ptx::tmem_ld32(tcol, ra);
-        ptx::tmem_ld32(tcol + 32, rb);
+        if (!issued) {
+          // warp-uniform outcome: the TMEM loads below need the whole warp converged
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(&sh->tmem_full[as], aphase, abort_flag))) { ok = false; break; }
+          ptx::tc_fence_after_sync();
+          ptx::tmem_ld32(tcol, ra);
+          ptx::tmem_ld32(tcol + 32, rb);
+        }
         ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[j] = fmaf(tmem_value<KIND>(ra[j]), s0, acc[j]);
+        promote32<KIND>(acc, ra, s0);
         ptx::tmem_ld32(tcol + 128, ra);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[32 + j] = fmaf(tmem_value<KIND>(rb[j]), s0, acc[32 + j]);
+        promote32<KIND>(acc + 32, rb, s0);
         ptx::tmem_ld32(tcol + 160, rb);
         ptx::tmem_ld_wait32(ra); ptx::tmem_ld_wait32(rb);
+        // the stage goes back to the MMA warp as soon as its last load has landed
         ptx::tc_fence_before_sync();
         __syncwarp();
         if (lane == 0) {
           if (PAIR && !leader) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_u32(&sh->tmem_empty[as]), 0));
           else ptx::mbar_arrive(&sh->tmem_empty[as]);
         }
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[64 + j] = fmaf(tmem_value<KIND>(ra[j]), s1, acc[64 + j]);
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc[96 + j] = fmaf(tmem_value<KIND>(rb[j]), s1, acc[96 + j]);
         if (++as == kAccStages) { as = 0; aphase ^= 1u; }
+        issued = false;
+        if (kb + 1 < KBp && __all_sync(0xffffffffu, ptx::mbar_try_wait(&sh->tmem_full[as], aphase))) {
+          const uint32_t ncol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
+          ptx::tc_fence_after_sync();
+          promote32<KIND>(acc + 64, ra, s1);
+          ptx::tmem_ld32(ncol, ra);
+          promote32<KIND>(acc + 96, rb, s1);
+          ptx::tmem_ld32(ncol + 32, rb);
+          issued = true;
+        } else {
+          promote32<KIND>(acc + 64, ra, s1);
+          promote32<KIND>(acc + 96, rb, s1);
+        }
       }
       if (!ok) break;
       if (t + nworkers < total_tiles) {

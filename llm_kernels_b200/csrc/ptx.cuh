@@ -274,6 +274,24 @@ __device__ __forceinline__ void tmem_ld_wait32(uint32_t (&r)[32]) {
       :
       : "memory");
 }
+// Two IEEE f32 fused multiply-adds in one instruction: (d0, d1) += (a0, a1) * (s.x, s.y), where `s2`
+// holds the two multipliers packed in 64 bits (pack_f32x2).  Per lane identical to fmaf().
+__device__ __forceinline__ uint64_t pack_f32x2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void ffma2(float& d0, float& d1, uint32_t a0, uint32_t a1, uint64_t s2) {
+  asm("{\n"
+      ".reg .b64 va, vc;\n"
+      "mov.b64 va, {%2, %3};\n"
+      "mov.b64 vc, {%0, %1};\n"
+      "fma.rn.f32x2 vc, va, %4, vc;\n"
+      "mov.b64 {%0, %1}, vc;\n"
+      "}\n"
+      : "+f"(d0), "+f"(d1)
+      : "r"(a0), "r"(a1), "l"(s2));
+}
 // Register budget hand-over between warpgroups (all 4 warps of a warpgroup execute it).
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {

@@ -159,7 +159,10 @@ class DeepseekV3MoE(nn.Module):
         # "nccl": all_to_all_single with split sizes; "push": peer copies on the copy engines;
         # "fused": records and results stored straight into the peers' buffers by the permute kernel
         # and the down projection (fp8_block only; no host read, no pipeline passes)
-        self.exchange = getattr(config, "ep_exchange", "nccl") if self.ep_size > 1 else "none"
+        # default ("auto"): "fused" for fp8_block, "nccl" for the int4 methods
+        self.exchange = getattr(config, "ep_exchange", "auto") if self.ep_size > 1 else "none"
+        if self.exchange == "auto":
+            self.exchange = "fused" if self.method == "fp8_block" else "nccl"
         assert self.exchange in ("nccl", "push", "fused", "none")
         if self.exchange == "fused":
             assert self.method == "fp8_block", "ep_exchange='fused' is built for quantize_method='fp8_block'"
