@@ -307,7 +307,9 @@ B200MOE_API int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_byte
  * b200moe_w4a16_expand_bf16).  a bf16 [M_total, K] (row stride in bytes), b bf16
  * [num_weights, N, K].  epilogue 0: c [M_total, N] f32/f16/bf16.  epilogue 2: SwiGLU
  * (moe/group_gemm_kernel.py:120-168) fused, b rows [0,N/2) gate and [N/2,N) up,
- * c bf16 [M_total, N/2].  K % 64 == 0, N % 128 == 0 (epilogue 2: N % 256 == 0). */
+ * c bf16 [M_total, N/2].  epilogue 3: c (f16/bf16) = round(c + round(a . b^T)), the sum formed when
+ * a module's output is added to a tensor of the same dtype (shared experts,
+ * moe/all2all_moe.py:182-183).  K % 64 == 0, N % 128 == 0 (epilogue 2: N % 256 == 0). */
 B200MOE_API int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
                               int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                               int64_t K, int num_groups, int num_weights,

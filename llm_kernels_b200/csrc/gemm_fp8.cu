@@ -85,6 +85,10 @@ struct GemmParams {
   // The addresses may lie in another GPU's memory (peer mapping): the rows then cross NVLink as
   // plain stores straight from the epilogue, and the kernel ends with a system-scope fence.
   const int64_t* c_row_addr;
+  // plain epilogue with a 16-bit output: c = round(c + round(product)), the sum a module computes
+  // when it adds this GEMM's output to a tensor of the same dtype (shared experts added to the
+  // routed output, moe/all2all_moe.py:182-183)
+  int accumulate;
 };
 
 struct Tile { int m0, m_end, expert, nt, ks; };
@@ -509,13 +513,33 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
             for (int i = 0; i < 4; ++i) {
               const int r = (lane >> 3) + 4 * i;               // row inside this 16-row part
               const int cc = lane & 7;
-              const uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((cc ^ (r & 7)) << 4));
+              uint4 val = *reinterpret_cast<const uint4*>(stg + r * 128 + ((cc ^ (r & 7)) << 4));
               const int orow_in = tl.m0 + q * 32 + part * 16 + r;
               if (orow_in < tl.m_end) {
                 const int64_t orow = p.c_row_map ? p.c_row_map[orow_in] : orow_in;
                 uint8_t* dst = p.c_row_addr ? reinterpret_cast<uint8_t*>(p.c_row_addr[orow_in])
                                             : static_cast<uint8_t*>(p.c) + tl.ks * p.split_stride + orow * p.c_stride;
-                *reinterpret_cast<uint4*>(dst + static_cast<int64_t>(col0) * 2 + cc * 16) = val;
+                uint4* out = reinterpret_cast<uint4*>(dst + static_cast<int64_t>(col0) * 2 + cc * 16);
+                if (p.accumulate) {
+                  const uint4 old = *out;
+                  const uint32_t* o = &old.x;
+                  uint32_t* n = &val.x;
+#pragma unroll
+                  for (int i2 = 0; i2 < 4; ++i2) {
+                    if (p.c_dtype == B200MOE_BF16) {
+                      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&o[i2]));
+                      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&n[i2]));
+                      const __nv_bfloat162 t2 = __floats2bfloat162_rn(a.x + b.x, a.y + b.y);
+                      n[i2] = *reinterpret_cast<const uint32_t*>(&t2);
+                    } else {
+                      const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&o[i2]));
+                      const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&n[i2]));
+                      const __half2 t2 = __floats2half2_rn(a.x + b.x, a.y + b.y);
+                      n[i2] = *reinterpret_cast<const uint32_t*>(&t2);
+                    }
+                  }
+                }
+                *out = val;
               }
             }
             __syncwarp();
@@ -658,7 +682,7 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
   if (M == 0) return B200MOE_OK;
   const int esz = c_dtype == B200MOE_F32 ? 4 : 2;
   GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
-               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr, nullptr};
+               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr, nullptr, 0};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
 }
@@ -699,7 +723,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
-               num_weights, c_dtype, epilogue, status_word, 1, 0, 0, c_row_map, c_row_addr};
+               num_weights, c_dtype, epilogue, status_word, 1, 0, 0, c_row_map, c_row_addr, 0};
   return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -734,7 +758,7 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
                   B200MOE_BAD_ARG, "grouped_gemm_i8: c row stride");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr, nullptr};
+               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr, nullptr, 0};
   return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -745,8 +769,10 @@ static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_byte
                               int epilogue, int32_t* status_word, void* stream) {
   if (int rc = check_grouped_common("grouped_gemm_bf16", a, b, c, seg_indptr, a_row_stride_bytes, 2 * K, M_total, N,
                                     num_groups, num_weights)) return rc;
-  B200MOE_REQUIRE(epilogue == 0 || (epilogue == 2 && !f16), B200MOE_BAD_ARG,
-                  "grouped_gemm_bf16: epilogue %d (0 plain, 2 SwiGLU with bf16 operands)", epilogue);
+  B200MOE_REQUIRE(epilogue == 0 || epilogue == 3 || (epilogue == 2 && !f16), B200MOE_BAD_ARG,
+                  "grouped_gemm_bf16: epilogue %d (0 plain, 2 SwiGLU with bf16 operands, 3 plain added to c)", epilogue);
+  B200MOE_REQUIRE(epilogue != 3 || c_dtype == B200MOE_BF16 || c_dtype == B200MOE_F16, B200MOE_BAD_DTYPE,
+                  "grouped_gemm_bf16: epilogue 3 adds into a 16-bit c");
   if (epilogue == 2) {
     B200MOE_REQUIRE(N % 256 == 0 && c_dtype == B200MOE_BF16 && c_row_stride_bytes >= N, B200MOE_BAD_ARG,
                     "grouped_gemm_bf16: the SwiGLU epilogue needs N %% 256 == 0 and a bf16 [M, N/2] output");
@@ -758,7 +784,8 @@ static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_byte
   B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0, B200MOE_BAD_ALIGN, "grouped_gemm_bf16: c row stride alignment");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue, status_word, 1, 0, 0, nullptr, nullptr};
+               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue == 3 ? 0 : epilogue,
+               status_word, 1, 0, 0, nullptr, nullptr, epilogue == 3 ? 1 : 0};
   return f16 ? launch_gemm<kF16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream))
              : launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
@@ -800,7 +827,7 @@ extern "C" int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_b
   if (T == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, partials, static_cast<int64_t>(E) * 4, nullptr, 0, nullptr, nullptr, T, E,
                static_cast<int>(3 * H * 2), 1, 1, B200MOE_F32, 0, nullptr, ksplits, T * static_cast<int64_t>(E) * 4,
-               static_cast<int>(H * 2), nullptr, nullptr};
+               static_cast<int>(H * 2), nullptr, nullptr, 0};
   const int64_t tiles = ((T + BM - 1) / BM) * ((E + BN - 1) / BN) * ksplits;
   return launch_gemm<kBf16>(x_bf16, H * 2, w3_bf16, p, tiles, as_stream(stream));
 }

@@ -159,8 +159,15 @@ class DeepseekV3MoE(nn.Module):
         # "nccl": all_to_all_single with split sizes; "push": peer copies on the copy engines;
         # "fused": records and results stored straight into the peers' buffers by the permute kernel
         # and the down projection (fp8_block only; no host read, no pipeline passes)
+        # "all2all": tokens are data-parallel and rows travel to their experts (reference
+        # moe/all2all_moe.py); "allreduce": every rank sees all tokens, runs its own experts on them and
+        # the outputs are summed across ranks (reference moe/sglang_moe_all_gather_all_reduce.py:267-446)
+        self.strategy = getattr(config, "ep_strategy", "all2all") if self.ep_size > 1 else "all2all"
+        assert self.strategy in ("all2all", "allreduce")
         # default ("auto"): "fused" for fp8_block, "nccl" for the int4 methods
         self.exchange = getattr(config, "ep_exchange", "auto") if self.ep_size > 1 else "none"
+        if self.strategy == "allreduce":
+            self.exchange, self.passes = "none", 1
         if self.exchange == "auto":
             self.exchange = "fused" if self.method == "fp8_block" else "nccl"
         assert self.exchange in ("nccl", "push", "fused", "none")
@@ -200,8 +207,15 @@ class DeepseekV3MoE(nn.Module):
             reg("w2_s4", z(El, H, I // 128, dtype=torch.int8))
             reg("w2_z4", z(El, H, I // 128, dtype=torch.int8))
         self.gate = MoEGate(config).to(dev)
-        if config.n_shared_experts:
-            raise NotImplementedError("shared experts are not built yet")
+        # Shared experts (reference :161-165, 182-183): one DeepseekV3MLP of width
+        # n_shared_experts * moe_intermediate_size applied to every token, unquantized as in the
+        # reference (plain bf16 nn.Linear layers there), added to the routed output.
+        self.n_shared = int(config.n_shared_experts or 0)
+        if self.n_shared:
+            Is = I * self.n_shared
+            reg("shared_w13", z(1, 2 * Is, H, dtype=torch.bfloat16))     # [gate_proj ; up_proj]
+            reg("shared_w2", z(1, H, Is, dtype=torch.bfloat16))          # down_proj
+            self._shared_stream = None
         self._buffers_cache = {}
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._last_recv_rows = None
@@ -243,6 +257,39 @@ class DeepseekV3MoE(nn.Module):
                 getattr(self, f"{name}_s4")[local_idx].copy_(s4)
                 getattr(self, f"{name}_z4")[local_idx].copy_(z4)
 
+    def load_shared_experts(self, gate_w: torch.Tensor, up_w: torch.Tensor, down_w: torch.Tensor):
+        """Weights of the shared DeepseekV3MLP: gate_proj/up_proj [I*n_shared, H], down_proj [H, I*n_shared]."""
+        assert self.n_shared, "config.n_shared_experts is 0"
+        self.shared_w13[0].copy_(torch.cat([gate_w, up_w], dim=0))
+        self.shared_w2[0].copy_(down_w)
+
+    def _shared_begin(self, x):
+        """gate/up projection + SwiGLU of the shared experts on a side stream: it needs only x, so it
+        fills the SMs while the routed path waits on its exchange.  Returns (h, event)."""
+        T, H = x.shape
+        Is = self.shared_w2.shape[2]
+        if self._shared_stream is None:
+            self._shared_stream = torch.cuda.Stream(device=self._dev)
+        side, main = self._shared_stream, torch.cuda.current_stream()
+        seg = self._buffers_cache.get(("shared_seg", T))
+        if seg is None:
+            seg = self._buffers_cache[("shared_seg", T)] = torch.tensor([0, T], dtype=torch.int64, device=self._dev)
+        h = self._buf("shared_h", (T, Is), torch.bfloat16)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            G.grouped_gemm_bf16(x, self.shared_w13, seg, None, h, epilogue=2, status_word=self._status)
+            ev = torch.cuda.Event()
+            ev.record(side)
+        return h, seg, ev
+
+    def _shared_finish(self, fork, y):
+        """down projection of the shared experts, added into the routed output in the GEMM's stores:
+        y = bf16(y + bf16(h @ w2^T)), the sum the reference forms at :183."""
+        h, seg, ev = fork
+        torch.cuda.current_stream().wait_event(ev)
+        G.grouped_gemm_bf16(h, self.shared_w2, seg, None, y, epilogue=3, status_word=self._status)
+        self._mark("shared_experts")
+
     def _buf(self, name, shape, dtype):
         t = self._buffers_cache.get(name)
         n = 1
@@ -263,7 +310,10 @@ class DeepseekV3MoE(nn.Module):
         x = hidden_states.reshape(-1, orig_shape[-1])
         if not x.is_contiguous():
             x = x.contiguous()
+        fork = self._shared_begin(x) if self.n_shared else None
         y = self.triton_group_gemm_moe_infer(x, topk_idx, topk_weight)
+        if self.n_shared:
+            self._shared_finish(fork, y)
         return y.view(*orig_shape)
 
     # the reference's unfused entry point routes to the same pipeline
@@ -296,6 +346,8 @@ class DeepseekV3MoE(nn.Module):
         # The exchange plan needs only the per-expert counts: its count all-to-all and its one host
         # read are issued before the permute kernel, which then runs while the host builds the plan.
         push = ep > 1 and self.exchange == "push"
+        if ep > 1 and self.strategy == "allreduce":
+            return self._run_allreduce(x, ids, topk_weight, src2dst, seg_indptr, T, H, k, E, rec)
         if ep > 1 and self.exchange == "fused":
             down = self._run_fused(x, ids, src2dst, seg_indptr, S, H, rec)
             out = torch.empty((T, H), dtype=x.dtype, device=x.device)
@@ -390,6 +442,36 @@ class DeepseekV3MoE(nn.Module):
     @last_recv_rows.setter
     def last_recv_rows(self, v):
         self._last_recv_rows = v
+
+    def _run_allreduce(self, x, ids, topk_weight, src2dst, seg_indptr, T, H, k, E, rec):
+        """Every rank holds all T tokens: permute + quantize only the slots of this rank's experts
+        (the start/end expert ids of reference sglang_moe_all_gather_all_reduce.py:312-324), run them,
+        un-permute into a partial output and sum the partial outputs over the ranks (:441-442)."""
+        El = self.experts_per_rank
+        lo, hi = self.ep_rank * El, self.ep_rank * El + El - 1
+        S = T * k
+        send = self._buf("send", (S, rec), torch.uint8)
+        if self.method == "fp8_block":
+            G.permute_quant_fp8(x, src2dst, ids, lo, hi, send[:, :H], send[:, H:H + (H // 128) * 4].view(torch.float32))
+        elif self.method == "w4a8":
+            G.permute_quant_int8(x, src2dst, ids, lo, hi, send[:, :H],
+                                 send[:, H:H + (H // 128) * 4].view(torch.float32), rounding="floor_half")
+        else:
+            G.pre_reorder_triton_kernel[(T,)](x, send.view(torch.bfloat16), src2dst, ids, None, lo, hi, k, H,
+                                              BLOCK_SIZE=512)
+        self._mark("permute_quant")
+        seg_local = seg_indptr[lo:hi + 2]                    # absolute row offsets of my experts' groups
+        down = self._buf("down", (S, H), torch.bfloat16)
+        self._last = (send, S, seg_local, None)
+        self._last_recv_rows = seg_local[-1] - seg_local[0]
+        if S > 0:
+            getattr(self, "_experts_" + self.method)({}, send, S, seg_local, None, down, (0, S))
+        out = torch.empty((T, H), dtype=x.dtype, device=x.device)
+        G.post_reorder_triton_kernel[(T,)](down, out, src2dst, ids, topk_weight, lo, hi, k, H, BLOCK_SIZE=512)
+        self._mark("post_reorder")
+        dist.all_reduce(out, op=dist.ReduceOp.SUM)
+        self._mark("all_reduce")
+        return out
 
     def _run_fused(self, x, ids, src2dst, seg_indptr, S, H, rec):
         """Exchange folded into the permute kernel and the down projection (ep_comm.FusedExchange)."""

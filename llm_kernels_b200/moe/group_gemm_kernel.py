@@ -226,7 +226,8 @@ def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=N
 
 def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, status_word=None):
     """tcgen05 grouped bf16 or f16 GEMM (reference: the scale-free branch of grouped_gemm_triton,
-    :410-412).  epilogue 0: c [M,N]; epilogue 2 (bf16 operands only): SwiGLU fused, c bf16 [M,N/2]."""
+    :410-412).  epilogue 0: c [M,N]; epilogue 2 (bf16 operands only): SwiGLU fused, c bf16 [M,N/2];
+    epilogue 3: c = round(c + round(a @ b^T)) for a 16-bit c."""
     N.require_cuda(a, b, c)
     assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)
     assert b.is_contiguous() and a.stride(1) == 1
@@ -234,7 +235,8 @@ def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, st
     W, Nn, Kb = b.shape
     assert Kb == K
     if a.dtype == torch.float16:
-        assert epilogue == 0, "the fused SwiGLU epilogue takes bf16 operands"
+        assert epilogue in (0, 3), "the fused SwiGLU epilogue takes bf16 operands"
+        assert epilogue == 0, "b200moe_grouped_gemm_f16 has the plain epilogue only"
         N.check(N.lib().b200moe_grouped_gemm_f16(
             N.ptr(a), a.stride(0) * 2, N.ptr(b), N.ptr(c), N.dtype_code(c.dtype), c.stride(0) * c.element_size(),
             M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices),

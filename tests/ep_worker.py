@@ -22,14 +22,17 @@ def main():
     torch.cuda.set_device(rank)
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", device_id=dev)
-    shape = replace(WL.CONFIG3, tokens=96 + 32 * rank, hidden=512, inter=256, experts=32, n_group=4,
-                    topk_group=2, top_k=4)
+    strategy = os.environ.get("EP_STRATEGY", "all2all")
+    # all-to-all: every rank routes its own (differently sized) batch; all-reduce: all ranks see one batch
+    shape = replace(WL.CONFIG3, tokens=96 + (32 * rank if strategy == "all2all" else 0), hidden=512, inter=256,
+                    experts=32, n_group=4, topk_group=2, top_k=4)
     cfg = WL.make_config(shape, ep_size=world)
+    cfg.ep_strategy = strategy
     cfg.ep_passes = int(os.environ.get("EP_PASSES", "1"))
     cfg.ep_exchange = os.environ.get("EP_EXCHANGE", "nccl")
     layer = DeepseekV3MoE(cfg, device=dev).eval()
     WL.fill_layer_cpu_seeded(layer, shape)
-    x = WL.tokens(shape, rank=rank)
+    x = WL.tokens(shape, rank=rank if strategy == "all2all" else 0)
     y = layer(x.to(dev).view(1, shape.tokens, -1))
     y = layer(x.to(dev).view(1, shape.tokens, -1))      # twice: buffers and peer mappings are re-used
     layer.check_status()
@@ -46,7 +49,8 @@ def main():
     y_ref = R.moe_layer_fp8(x, idx, w, torch.stack([a for a, _ in q13]), torch.stack([s for _, s in q13]),
                             torch.stack([a for a, _ in q2]), torch.stack([s for _, s in q2]), ep_size=world)
     err = R.rel_fro(y.cpu().view(shape.tokens, -1).float(), y_ref.float())
-    rows = torch.tensor([layer.last_recv_rows, shape.tokens * shape.top_k], device=dev)
+    own = shape.tokens * shape.top_k if strategy == "all2all" or rank == 0 else 0
+    rows = torch.tensor([layer.last_recv_rows, own], device=dev)
     dist.all_reduce(rows)
     assert int(rows[0]) == int(rows[1]), "rows are not conserved across the exchange"
     assert err < 1e-2, f"rank {rank}: rel_fro {err}"

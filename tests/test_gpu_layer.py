@@ -169,3 +169,51 @@ def test_layer_w4a8_decode_shape_reduced():
     layer.check_status()
     err = R.rel_fro(y.cpu().float(), y_ref.float())
     assert err < 1e-2, err
+
+
+@pytest.mark.parametrize("n_shared", [1, 2])
+def test_layer_with_shared_experts(n_shared):
+    """config.n_shared_experts (reference moe/all2all_moe.py:161-165, 182-183): an unquantized bf16
+    DeepseekV3MLP of width n_shared * I on every token, added to the routed output in bf16."""
+    from llm_kernels_b200 import workloads as WL
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+    from dataclasses import replace
+    dev = torch.device("cuda:0")
+    shape = replace(WL.CONFIG0, tokens=200, hidden=512, inter=256, seed=77)
+    x = WL.tokens(shape)
+    _, _, y_routed, _ = _oracle_layer(shape, x)
+    g = torch.Generator().manual_seed(5)
+    Is = shape.inter * n_shared
+    gw = (torch.randn(Is, shape.hidden, generator=g) * 0.05).to(torch.bfloat16)
+    uw = (torch.randn(Is, shape.hidden, generator=g) * 0.05).to(torch.bfloat16)
+    dw = (torch.randn(shape.hidden, Is, generator=g) * 0.05).to(torch.bfloat16)
+    y_ref = y_routed + R.expert_mlp(x, gw, uw, dw)            # bf16 module arithmetic, as the reference
+    cfg = WL.make_config(shape)
+    cfg.n_shared_experts = n_shared
+    layer = DeepseekV3MoE(cfg, device=dev).eval()
+    WL.fill_layer_cpu_seeded(layer, shape)
+    layer.load_shared_experts(gw.to(dev), uw.to(dev), dw.to(dev))
+    for _ in range(2):
+        y = layer(x.to(dev).view(1, shape.tokens, -1))
+    layer.check_status()
+    shared_only = R.expert_mlp(x, gw, uw, dw).float()
+    assert shared_only.norm() > 0.2 * y_routed.float().norm()         # the shared term is not negligible here
+    assert R.rel_fro(y.cpu().view(shape.tokens, -1).float(), y_ref.float()) < 1e-2
+
+
+def test_grouped_gemm_bf16_accumulate_epilogue():
+    """epilogue 3: c = bf16(c + bf16(a @ b^T)), bit-exact against the same sum formed by torch."""
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    dev = torch.device("cuda:0")
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 200, 256, 192
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    b = (torch.randn(1, N, K, generator=g) * 0.1).to(torch.bfloat16).to(dev)
+    c0 = torch.randn(M, N, generator=g).to(torch.bfloat16).to(dev)
+    seg = torch.tensor([0, M], dtype=torch.int64, device=dev)
+    plain = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    G.grouped_gemm_bf16(a, b, seg, None, plain, epilogue=0)
+    c = c0.clone()
+    G.grouped_gemm_bf16(a, b, seg, None, c, epilogue=3)
+    torch.cuda.synchronize()
+    assert torch.equal(c, c0 + plain)
