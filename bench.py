@@ -40,7 +40,7 @@ NOMINAL_HBM_GBS = 8000.0
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE gate/up launch in the ncu capture summarised in
 # profiles/gemm_block_kernel_fp8_cfg3_small.md (32 experts, 4096 rows).  At EP = 1 the full workload has
 # 8x the experts and 8x the rows, and the traffic (weights once + rows once) grows in proportion.
-NCU_GEMM1_SMALL = {"dram_bytes": 1027.476e6 + 14.200832e6, "experts": 32, "rows": 4096}
+NCU_GEMM1_SMALL = {"dram_bytes": 1026.601e6 + 16.708864e6, "experts": 32, "rows": 4096}
 
 
 def _peaks():
