@@ -266,9 +266,8 @@ B200MOE_API int b200moe_set_gemm_max_ctas(int max_ctas);
 
 /* No counterpart in the reference.  Tile shape of the grouped/dense GEMMs above: 0 = one CTA per
  * 128 x 256 tile, 1 = clusters of two CTAs sharing a 256 x 256 tile (tcgen05 cta_group::2; each
- * SM then moves 32 KB instead of 48 KB per K block through the crossbar).  Default 0: pairs are
- * slower for the kinds that promote every K block (the stage hand-over crosses SMs).  Results are
- * identical in both modes. */
+ * SM then moves 32 KB instead of 48 KB per K block through the crossbar).  Default 0: measured
+ * within +-5 % of single-CTA tiles for every kind.  Results are identical in both modes. */
 B200MOE_API int b200moe_set_gemm_pair_mode(int mode);
 
 /* ===================== int4 weight paths (w4a8, w4a16) ==================== */

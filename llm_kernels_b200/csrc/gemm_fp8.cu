@@ -616,8 +616,11 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
 // (registers and shared memory), so a collective that should run concurrently needs SMs left free.
 static int g_max_ctas = 0;
 // CTA pairs (256-row tiles): 0 = off (default), 1 = on.  Measured on B200 with 32 groups x 1024
-// rows: bf16/f16 operands gain 5 % from pairs, while the kinds that promote every K block lose
-// 45 % (1.6 -> 0.9 PFLOP/s): the tensor-memory stage hand-over then crosses SMs twice per K block.
+// rows: bf16/f16 operands gain 5 % from pairs; the kinds that promote every K block come out within
+// 3 % of single-CTA tiles either way (they are bound by the tensor-memory read-back, not by the
+// 48 KB vs 32 KB per K block that pairs save), once the peer's stage hand-over is a RELAXED
+// cluster-scope arrive: as a release it waited for the thread's earlier global stores and loads
+// and halved the throughput.
 static int g_pair_mode = 0;
 
 template <int KIND, bool PAIR>
