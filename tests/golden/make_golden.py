@@ -101,6 +101,25 @@ def main():
     put("moe_dense", x=x.view(-1, 64), gate_W=model.gate.weight.detach(), gate_w=gw, up_w=uw,
         down_w=dw, topk_idx=idx, topk_weight=w, y=y.view(-1, 64))
 
+    # ---------------- same with shared experts (moe/all2all_moe.py:161-165, 182-183) ----
+    cfg.n_shared_experts = 2
+    model_s = ref_a2a.DeepseekV3MoE(cfg).eval()
+    g2 = torch.Generator().manual_seed(22)
+    with torch.no_grad():
+        model_s.gate.weight.copy_(model.gate.weight)
+        for e in range(8):
+            model_s.experts[e].gate_proj.weight.copy_(gw[e])
+            model_s.experts[e].up_proj.weight.copy_(uw[e])
+            model_s.experts[e].down_proj.weight.copy_(dw[e])
+        sg = torch.randn(64, 64, generator=g2) * 0.1
+        su = torch.randn(64, 64, generator=g2) * 0.1
+        sd = torch.randn(64, 64, generator=g2) * 0.1
+        model_s.shared_experts.gate_proj.weight.copy_(sg)
+        model_s.shared_experts.up_proj.weight.copy_(su)
+        model_s.shared_experts.down_proj.weight.copy_(sd)
+        y_s = model_s(x)
+    put("moe_dense_shared", shared_gate_w=sg, shared_up_w=su, shared_down_w=sd, y=y_s.view(-1, 64))
+
     # ---------------- run_moe_ep_preproess (moe/group_gemm_kernel.py:48-78) -----------
     for case, (T, k, E, seed) in {"prep_small": (6, 2, 4, 31), "prep_skew": (200, 8, 64, 32),
                                   "prep_empty_experts": (33, 2, 32, 33)}.items():

@@ -40,6 +40,16 @@ def test_moe_dense_matches_reference(golden):
     torch.testing.assert_close(y, t(c["y"]), rtol=1e-5, atol=1e-6)
 
 
+def test_moe_dense_with_shared_experts_matches_reference(golden):
+    """DeepseekV3MoE.forward with n_shared_experts = 2 (moe/all2all_moe.py:161-165, 182-183): the routed
+    output plus one DeepseekV3MLP of width 2 * moe_intermediate_size on every token."""
+    c, cs = golden.case("moe_dense"), golden.case("moe_dense_shared")
+    x = t(c["x"])
+    y = R.moe_infer_dense(x, t(c["topk_idx"]), t(c["topk_weight"]), t(c["gate_w"]), t(c["up_w"]), t(c["down_w"]))
+    y = y + R.expert_mlp(x, t(cs["shared_gate_w"]), t(cs["shared_up_w"]), t(cs["shared_down_w"]))
+    torch.testing.assert_close(y, t(cs["y"]), rtol=1e-5, atol=1e-6)
+
+
 @pytest.mark.parametrize("case", ["prep_small", "prep_skew", "prep_empty_experts"])
 def test_preprocess_bit_exact(golden, case):
     c = golden.case(case)
