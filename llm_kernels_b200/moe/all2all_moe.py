@@ -316,6 +316,36 @@ class DeepseekV3MoE(nn.Module):
             self._shared_finish(fork, y)
         return y.view(*orig_shape)
 
+    def make_graphed(self, example: torch.Tensor, warmup: int = 2):
+        """Captures one forward pass for inputs of `example`'s shape and dtype into a CUDA graph and
+        returns `run(x) -> y`.  The layer's launch sequence is fixed and reads nothing back to the host
+        (with expert parallelism: ep_exchange="fused" or the all-reduce strategy, whose collectives are
+        captured with it, so every rank must call `run` the same number of times).  For small batches,
+        where the step is a dozen launches of a few microseconds each, replaying the graph removes the
+        per-launch host cost.  `y` is a static buffer that the next `run` overwrites; a device-side
+        timeout or a receive-buffer overflow still shows up in `check_status()`."""
+        assert self.ep_size == 1 or self.exchange == "fused" or self.strategy == "allreduce", \
+            "the nccl and push exchanges read split sizes back to the host and cannot be captured"
+        cur = torch.cuda.current_stream()
+        side = torch.cuda.Stream(device=self._dev)
+        static_in = example.detach().clone()
+        side.wait_stream(cur)
+        with torch.cuda.stream(side):              # warm-up: buffers, peer mappings, driver entry points
+            for _ in range(max(warmup, 1)):
+                self(static_in)
+        cur.wait_stream(side)
+        torch.cuda.synchronize(self._dev)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            static_out = self(static_in)
+
+        def run(x: torch.Tensor) -> torch.Tensor:
+            static_in.copy_(x, non_blocking=True)
+            graph.replay()
+            return static_out
+        run.graph, run.static_input, run.static_output = graph, static_in, static_out
+        return run
+
     # the reference's unfused entry point routes to the same pipeline
     def moe_infer(self, x, topk_ids, topk_weight):
         return self.triton_group_gemm_moe_infer(x, topk_ids, topk_weight)

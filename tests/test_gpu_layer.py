@@ -217,3 +217,30 @@ def test_grouped_gemm_bf16_accumulate_epilogue():
     G.grouped_gemm_bf16(a, b, seg, None, c, epilogue=3)
     torch.cuda.synchronize()
     assert torch.equal(c, c0 + plain)
+
+
+@pytest.mark.parametrize("T,n_shared", [(64, 0), (200, 1)])
+def test_layer_cuda_graph_replay_matches_eager(T, n_shared):
+    """make_graphed: the captured launch sequence replayed on new inputs gives the eager result bit for bit."""
+    from llm_kernels_b200 import workloads as WL
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+    from dataclasses import replace
+    dev = torch.device("cuda:0")
+    shape = replace(WL.CONFIG0, tokens=T, hidden=512, inter=256, seed=90 + T)
+    cfg = WL.make_config(shape)
+    cfg.n_shared_experts = n_shared
+    layer = DeepseekV3MoE(cfg, device=dev).eval()
+    WL.fill_layer_cpu_seeded(layer, shape)
+    if n_shared:
+        g = torch.Generator().manual_seed(6)
+        Is = shape.inter * n_shared
+        layer.load_shared_experts(*[(torch.randn(*s, generator=g) * 0.05).to(torch.bfloat16).to(dev)
+                                    for s in ((Is, shape.hidden), (Is, shape.hidden), (shape.hidden, Is))])
+    xs = [WL.tokens(shape, rank=i).to(dev).view(1, T, -1) for i in range(3)]
+    run = layer.make_graphed(xs[0])
+    for x in xs[::-1]:
+        y_graph = run(x).clone()
+        y_eager = layer(x)
+        torch.cuda.synchronize()
+        assert torch.equal(y_graph, y_eager)
+    layer.check_status()
