@@ -326,6 +326,8 @@ def run_ours(args):
             stages[n1] = stages.get(n1, 0.0) + e0.elapsed_time(e1)
     stages = {n: v / args.steps for n, v in stages.items()}
     rows = layer.last_recv_rows
+    seg_last = layer._last[2]                                   # group table of the last forward on this rank
+    active = int(((seg_last[1:] - seg_last[:-1]) > 0).sum().item())   # experts that received rows
     barrier()
     g1_ms, g2_ms, _ = layer.time_expert_gemms(max(3, min(args.steps, 10)))   # kernels alone, all groups
     barrier()
@@ -335,10 +337,11 @@ def run_ours(args):
         tokens_per_s = world * T * args.steps / (ms * 1e-3)
         e2e_tokens_per_s = world * T * args.steps / (ms_e2e * 1e-3)
         El, I = shape.experts // world, shape.inter
-        # dominant kernel: gate/up grouped GEMM.  Algorithmic bytes per launch: every local expert's
-        # w13 (e4m3) + its f32 block scales once, the activation rows (packed e4m3 + f32 scales) once,
-        # the e4m3 SwiGLU output + scales once.
-        g1_bytes = (El * (2 * I * H + (2 * I // 128) * (H // 128) * 4) + rows * (H + H // 32) + rows * (I + I // 32))
+        # dominant kernel: gate/up grouped GEMM.  Algorithmic bytes per launch: the w13 (e4m3) + f32 block
+        # scales of every local expert THAT RECEIVED ROWS once (experts without rows are skipped by the
+        # kernel and must not be credited), the activation rows (packed e4m3 + f32 scales) once, the e4m3
+        # SwiGLU output + scales once.
+        g1_bytes = (active * (2 * I * H + (2 * I // 128) * (H // 128) * 4) + rows * (H + H // 32) + rows * (I + I // 32))
         g1_flops = 4.0 * H * I * rows
         g2_flops = 2.0 * H * I * rows
         stages["gemm1_alone"], stages["gemm2_alone"] = g1_ms, g2_ms
@@ -353,9 +356,12 @@ def run_ours(args):
             ach = g1_bytes / g1_s / 1e9
             roof = {"kernel": "gemm_block_kernel<fp8> (gate/up + SwiGLU epilogue)", "bound": "hbm", "achieved": ach,
                     "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
-                    "traffic": NCU_GEMM1_SMALL["dram_bytes"] * El / NCU_GEMM1_SMALL["experts"]
+                    # ncu DRAM bytes of the 32-expert capture (all 32 active), scaled by the experts that stream
+                    # weights here: traffic is weight-dominated and grows in proportion
+                    "traffic": NCU_GEMM1_SMALL["dram_bytes"] * active / NCU_GEMM1_SMALL["experts"]
                     if rows == NCU_GEMM1_SMALL["rows"] * El // NCU_GEMM1_SMALL["experts"] else None,
-                    "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": g1_bytes}
+                    "peak_source": f"{peaks['source']} copy bandwidth", "algorithmic_bytes": g1_bytes,
+                    "active_experts": active}
         else:
             ach = g1_flops / g1_s / 1e12
             roof = {"kernel": "gemm_block_kernel<fp8> (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": ach,

@@ -113,13 +113,17 @@ __global__ void __launch_bounds__(256) ep_back_addr_kernel(const int32_t* __rest
 
 constexpr int kMaxTopK = 32;
 
-// One CTA per token (as permute_quant_fp8): the record of slot j goes to
-// dst_base[e] + (src2dst[slot] - seg[e]) * rec_bytes, payload first, then the f32 scales at byte H.
+// One CTA per token (as permute_quant_fp8).  The token's record (payload, then the f32 scales at
+// byte H) is built ONCE in shared memory and then copied to each of its destinations,
+// dst_base[e] + (src2dst[slot] - seg[e]) * rec_bytes, by one bulk asynchronous copy per destination:
+// a record crosses NVLink as a few large writes issued by the copy hardware instead of hundreds of
+// 8-byte stores from the SM.
 template <typename TI>
 __global__ void __launch_bounds__(256) permute_quant_fp8_push_kernel(
     const TI* __restrict__ x, const int32_t* __restrict__ src2dst, const int64_t* __restrict__ topk_ids,
     const int64_t* __restrict__ seg, const int64_t* __restrict__ dst_base, int num_experts, int topk,
     int64_t H, int64_t rec_bytes) {
+  extern __shared__ __align__(128) uint8_t s_rec[];
   __shared__ int64_t s_addr[kMaxTopK];
   __shared__ int s_n;
   const int64_t t = blockIdx.x;
@@ -154,15 +158,21 @@ __global__ void __launch_bounds__(256) permute_quant_fp8_push_kernel(
     float q[8];
 #pragma unroll
     for (int k = 0; k < 8; ++k) q[k] = __fdiv_rn(v[k], scale);
-    const uint2 packed = pack8_e4m3(q);
-    const bool lead = (threadIdx.x & 15) == 0;
-    for (int j = 0; j < n; ++j) {
-      uint8_t* rec = reinterpret_cast<uint8_t*>(s_addr[j]);
-      *reinterpret_cast<uint2*>(rec + i * 8) = packed;
-      if (lead) *reinterpret_cast<float*>(rec + H + (i / 16) * 4) = scale;
-    }
+    *reinterpret_cast<uint2*>(s_rec + i * 8) = pack8_e4m3(q);
+    if ((threadIdx.x & 15) == 0) *reinterpret_cast<float*>(s_rec + H + (i / 16) * 4) = scale;
   }
-  __threadfence_system();     // the records are read by another GPU after a stream-ordered barrier
+  for (int64_t b = H + (H / 128) * 4 + threadIdx.x; b < rec_bytes; b += blockDim.x) s_rec[b] = 0;   // padding
+  // make the generic-proxy writes visible to the bulk-copy engine, then one copy per destination
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  __syncthreads();
+  if (static_cast<int>(threadIdx.x) < n) {
+    const uint32_t src = static_cast<uint32_t>(__cvta_generic_to_shared(s_rec));
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;"
+                 ::"l"(s_addr[threadIdx.x]), "r"(src), "r"(static_cast<uint32_t>(rec_bytes)) : "memory");
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // the copy has been performed, not only read
+    __threadfence_system();     // the records are read by another GPU after a stream-ordered barrier
+  }
 }
 
 }  // namespace b200moe
@@ -223,17 +233,20 @@ extern "C" int b200moe_permute_quant_fp8_push(const void* x, int x_dtype, const 
   const int64_t chunks = H / 8;
   const int th = chunks >= 256 ? 256 : static_cast<int>((chunks + 31) / 32 * 32);
   const unsigned grid = static_cast<unsigned>(T);
+  const size_t smem = static_cast<size_t>(rec_bytes);
+  B200MOE_REQUIRE(rec_bytes <= 40 * 1024, B200MOE_BAD_SHAPE, "permute_quant_fp8_push: record of %lld bytes (max 40960)",
+                  (long long)rec_bytes);
   switch (x_dtype) {
     case B200MOE_BF16:
-      permute_quant_fp8_push_kernel<__nv_bfloat16><<<grid, th, 0, st>>>(static_cast<const __nv_bfloat16*>(x), src2dst, topk_ids,
+      permute_quant_fp8_push_kernel<__nv_bfloat16><<<grid, th, smem, st>>>(static_cast<const __nv_bfloat16*>(x), src2dst, topk_ids,
                                                                         seg_indptr, dst_base, num_experts, topk, H, rec_bytes);
       break;
     case B200MOE_F16:
-      permute_quant_fp8_push_kernel<__half><<<grid, th, 0, st>>>(static_cast<const __half*>(x), src2dst, topk_ids,
+      permute_quant_fp8_push_kernel<__half><<<grid, th, smem, st>>>(static_cast<const __half*>(x), src2dst, topk_ids,
                                                                  seg_indptr, dst_base, num_experts, topk, H, rec_bytes);
       break;
     case B200MOE_F32:
-      permute_quant_fp8_push_kernel<float><<<grid, th, 0, st>>>(static_cast<const float*>(x), src2dst, topk_ids,
+      permute_quant_fp8_push_kernel<float><<<grid, th, smem, st>>>(static_cast<const float*>(x), src2dst, topk_ids,
                                                                 seg_indptr, dst_base, num_experts, topk, H, rec_bytes);
       break;
     default:
