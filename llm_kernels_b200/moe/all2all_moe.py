@@ -503,6 +503,16 @@ class DeepseekV3MoE(nn.Module):
         self._mark("all_reduce")
         return out
 
+    def share_exchange_buffers(self, other: "DeepseekV3MoE"):
+        """Uses `other`'s peer-mapped receive/return buffers (ep_exchange="fused") instead of allocating
+        this layer's own: layers that run one after the other on a stream can share one pair (≈ 1 GB per
+        rank at 4096 tokens, hidden 7168), because the two barriers of a forward pass already order a
+        layer's reads before the next layer's remote writes.  Call after `other`'s first forward."""
+        assert self.exchange == "fused" and other.exchange == "fused" and other._fx is not None
+        assert (self.config.hidden_size, self.config.n_routed_experts, self.ep_size) == \
+               (other.config.hidden_size, other.config.n_routed_experts, other.ep_size)
+        self._fx = other._fx
+
     def _run_fused(self, x, ids, src2dst, seg_indptr, S, H, rec):
         """Exchange folded into the permute kernel and the down projection (ep_comm.FusedExchange)."""
         ep, E = self.ep_size, self.config.n_routed_experts

@@ -37,6 +37,15 @@ def main():
     y = layer(x.to(dev).view(1, shape.tokens, -1))      # twice: buffers and peer mappings are re-used
     layer.check_status()
     torch.cuda.synchronize()
+    if layer.exchange == "fused":
+        # a second layer on the first one's peer buffers (layers of a model run one after the other)
+        layer2 = DeepseekV3MoE(cfg, device=dev).eval()
+        WL.fill_layer_cpu_seeded(layer2, shape)
+        layer2.share_exchange_buffers(layer)
+        y2 = layer2(x.to(dev).view(1, shape.tokens, -1))
+        y1 = layer(x.to(dev).view(1, shape.tokens, -1))
+        layer2.check_status()
+        assert torch.equal(y2, y) and torch.equal(y1, y), "shared peer buffers changed the result"
 
     W, bias = WL.router_params(shape)
     kw = dict(top_k=shape.top_k, n_group=shape.n_group, topk_group=shape.topk_group, scoring_func=shape.scoring)
