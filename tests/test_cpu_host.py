@@ -182,3 +182,18 @@ def test_marlin_quantutils_match_reference_vectors(golden):
         assert torch.equal(sc, f("scale", torch.float16))
         pk, ps = QuantUtils.pack(q, sc, gs)
         assert torch.equal(pk, f("packed", torch.int32)) and torch.equal(ps, f("packed_scale", torch.float16))
+
+
+def test_marlin_mul_rejects_like_the_reference_binding():
+    """Argument checks of fast_dequant/simple_marlin/marlin_w4a16_gemm.cpp:38-88 happen before any launch,
+    so they can be exercised without a GPU."""
+    import pytest
+    from llm_kernels_b200.fast_dequant.simple_marlin import mul
+    A = torch.zeros(16, 128, dtype=torch.half)
+    B = torch.zeros(8, 128, dtype=torch.int32)
+    C = torch.zeros(16, 64, dtype=torch.half)
+    s = torch.ones(1, 64, dtype=torch.half)
+    with pytest.raises(RuntimeError, match="divisible by 16"):
+        mul(A[:15], B, C[:15], s, None)
+    with pytest.raises(RuntimeError, match="same CUDA device"):
+        mul(A, B, C, s, None)                   # CPU tensors: there is no CPU path
