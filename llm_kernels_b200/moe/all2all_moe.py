@@ -318,14 +318,13 @@ class DeepseekV3MoE(nn.Module):
 
     def make_graphed(self, example: torch.Tensor, warmup: int = 2):
         """Captures one forward pass for inputs of `example`'s shape and dtype into a CUDA graph and
-        returns `run(x) -> y`.  The layer's launch sequence is fixed and reads nothing back to the host
-        (with expert parallelism: ep_exchange="fused" or the all-reduce strategy, whose collectives are
-        captured with it, so every rank must call `run` the same number of times).  For small batches,
-        where the step is a dozen launches of a few microseconds each, replaying the graph removes the
-        per-launch host cost.  `y` is a static buffer that the next `run` overwrites; a device-side
-        timeout or a receive-buffer overflow still shows up in `check_status()`."""
-        assert self.ep_size == 1 or self.exchange == "fused" or self.strategy == "allreduce", \
-            "the nccl and push exchanges read split sizes back to the host and cannot be captured"
+        returns `run(x) -> y` (single-rank layers).  The layer's launch sequence is fixed and reads nothing
+        back to the host.  For small batches, where the step is a dozen launches of a few microseconds
+        each, replaying the graph removes the per-launch host cost.  `y` is a static buffer that the next
+        `run` overwrites; a device-side timeout still shows up in `check_status()`.  With expert
+        parallelism the step contains NCCL collectives; capturing those together with the peer-mapped
+        buffers did not complete on a 2-GPU trial (the ranks blocked in capture), so it is refused."""
+        assert self.ep_size == 1, "make_graphed supports ep_size == 1"
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream(device=self._dev)
         static_in = example.detach().clone()
