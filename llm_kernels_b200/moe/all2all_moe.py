@@ -33,6 +33,51 @@ from .config import Config  # noqa: F401  (re-exported like the reference does)
 from .utils import ResultCollector  # noqa: F401
 
 
+class DeepseekV3MLP(nn.Module):
+    """reference :13-29: ``down_proj(act_fn(gate_proj(x)) * up_proj(x))`` with three bias-free
+    nn.Linear layers (weights [out, in]).  Same constructor and parameter names; the forward pass
+    of a bf16 module on the GPU is two tcgen05 GEMMs, the first with SiLU(gate)*up fused in its
+    epilogue with the roundings a bf16 torch module produces."""
+
+    def __init__(self, config, hidden_size=None, intermediate_size=None):
+        super().__init__()
+        self.config = config
+        self.hidden_size = config.hidden_size if hidden_size is None else hidden_size
+        self.intermediate_size = config.intermediate_size if intermediate_size is None else intermediate_size
+        if getattr(config, "hidden_act", "silu") != "silu":
+            raise NotImplementedError("the fused epilogue implements silu")
+        self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
+        self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
+        self._w13_key = None
+
+    def _fused_gate_up(self):
+        g, u = self.gate_proj.weight, self.up_proj.weight
+        key = (g.data_ptr(), g._version, u.data_ptr(), u._version)
+        if self._w13_key != key:
+            self._w13 = torch.cat([g.detach(), u.detach()], dim=0).unsqueeze(0).contiguous()
+            self._w13_key = key
+        return self._w13
+
+    @torch.no_grad()
+    def forward(self, x):
+        N.require_cuda(x, self.gate_proj.weight)
+        assert x.dtype == torch.bfloat16 and self.gate_proj.weight.dtype == torch.bfloat16, \
+            "DeepseekV3MLP runs as a bfloat16 module (module.to(torch.bfloat16))"
+        H, I = self.hidden_size, self.intermediate_size
+        assert H % 128 == 0 and I % 128 == 0, "hidden and intermediate sizes must be multiples of 128"
+        x2 = x.reshape(-1, H)
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        M = x2.shape[0]
+        seg = torch.tensor([0, M], dtype=torch.int64, device=x.device)
+        h = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
+        G.grouped_gemm_bf16(x2, self._fused_gate_up(), seg, None, h, epilogue=2)
+        y = torch.empty(M, H, dtype=torch.bfloat16, device=x.device)
+        G.grouped_gemm_bf16(h, self.down_proj.weight.detach().unsqueeze(0), seg, None, y, epilogue=0)
+        return y.view(*x.shape[:-1], H)
+
+
 class MoEGate(nn.Module):
     """Router (reference :31-118): f32 logits, sigmoid (or softmax) scores, optional
     e_score_correction_bias, group-limited top-k, renormalisation, scaling."""

@@ -244,3 +244,20 @@ def test_layer_cuda_graph_replay_matches_eager(T, n_shared):
         torch.cuda.synchronize()
         assert torch.equal(y_graph, y_eager)
     layer.check_status()
+
+
+def test_deepseek_v3_mlp_matches_torch_module():
+    """DeepseekV3MLP (reference moe/all2all_moe.py:13-29) as a bf16 module: same parameters, output within
+    bf16 rounding of the torch module evaluated on the CPU."""
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MLP
+    from llm_kernels_b200.moe.config import Config
+    dev = torch.device("cuda:0")
+    cfg = Config()
+    torch.manual_seed(11)
+    mlp = DeepseekV3MLP(cfg, hidden_size=512, intermediate_size=384).to(torch.bfloat16)
+    x = torch.randn(3, 50, 512).to(torch.bfloat16)
+    want = R.expert_mlp(x.view(-1, 512), mlp.gate_proj.weight.detach(), mlp.up_proj.weight.detach(),
+                        mlp.down_proj.weight.detach())
+    got = mlp.to(dev)(x.to(dev))
+    assert got.shape == (3, 50, 512) and got.dtype == torch.bfloat16
+    assert R.rel_fro(got.cpu().view(-1, 512).float(), want.float()) < 3e-3
