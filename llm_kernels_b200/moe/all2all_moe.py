@@ -412,7 +412,7 @@ class DeepseekV3MoE(nn.Module):
         ep = self.ep_size
         # With expert parallelism the experts are visited in (pass, owner rank, expert-in-pass)
         # order so that every pipeline pass is contiguous on both sides of the exchange.
-        ids = topk_ids if ep == 1 else self._expert_order()[topk_ids]
+        ids = topk_ids if ep == 1 or self.passes == 1 else self._expert_order()[topk_ids]   # one pass: identity
         reorder_ids, src2dst, seg_indptr = G.run_moe_ep_preproess(ids, E)
         self._mark("route_metadata")
         rec = self._record_bytes(H)
