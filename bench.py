@@ -232,8 +232,13 @@ def run_ours(args):
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world} (launch with torch.distributed.run)"
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    # stdout carries ONE JSON line.  Libraries that write to file descriptor 1 on their own (NCCL prints its
+    # version banner there) are sent to stderr for the duration of the run; the line is printed on the saved
+    # descriptor at the end.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if world > 1:
-        os.environ["NCCL_DEBUG"] = "WARN"        # keep NCCL's version banner off stdout (one JSON line only)
         dist.init_process_group("nccl", device_id=dev)
     shape = WL.CONFIG3 if args.shape == "cfg3" else WL.CONFIG3_SMALL
     T, H, k = shape.tokens, shape.hidden, shape.top_k
@@ -395,7 +400,9 @@ def run_ours(args):
                 "sample": f"{args.cpu_tokens} of {T} tokens, all {shape.experts} experts (dequantized bf16 copies of the "
                           f"same weights), torch CPU per-expert loop, median of 2 after 1 warm-up "
                           f"({time.perf_counter() - t0:.0f} s incl. setup)"}
-        print(json.dumps(line), flush=True)
+        sys.stdout.flush()
+        os.write(json_fd, (json.dumps(line) + "\n").encode())
+    os.close(json_fd)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
