@@ -86,6 +86,16 @@ B200MOE_API int b200moe_gemm_fp8_block(const void* a, const float* a_s, const vo
                            void* c, int c_dtype, int64_t M, int64_t N, int64_t K,
                            void* stream);
 
+/* Same product with the K loop split over `ksplits` sets of tiles, for small M: one m-tile times
+ * N/256 n-tiles keeps only N/256 SMs streaming the weights, ksplits times as many tiles keep the
+ * chip busy.  Each split writes f32 partial products to `partials` (caller-owned scratch of
+ * ksplits * M * N * 4 bytes, 16-byte aligned); a second kernel adds them in split order and
+ * casts to c_dtype.  ceil(K/128 / ksplits) * (ksplits - 1) < K/128 (no empty split), ksplits <= 16.
+ * No counterpart in the reference. */
+B200MOE_API int b200moe_gemm_fp8_block_splitk(const void* a, const float* a_s, const void* b, const float* b_s,
+                                  void* c, int c_dtype, int64_t M, int64_t N, int64_t K, int ksplits,
+                                  float* partials, int64_t partials_bytes, void* stream);
+
 /* ======================= quantization/int8_kernel.py ====================== */
 
 /* act_quant: s = amax/127 stored as f16, y = round(x/s) as int8.

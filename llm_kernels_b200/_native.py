@@ -32,6 +32,7 @@ SIGNATURES = {
     "b200moe_weight_dequant_fp8": (_i, [_p, _p, _p, _i, _i64, _i64, _p]),
     "b200moe_weight_quant_fp8": (_i, [_p, _i, _p, _p, _i64, _i64, _p]),
     "b200moe_gemm_fp8_block": (_i, [_p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _p]),
+    "b200moe_gemm_fp8_block_splitk": (_i, [_p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p, _i64, _p]),
     "b200moe_act_quant_int8": (_i, [_p, _i, _i64, _i64, _p, _p, _i, _p]),
     "b200moe_router_topk": (_i, [_p, _i, _p, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p]),
     "b200moe_router_logits_bf16x3": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),

@@ -28,6 +28,8 @@
 // writes B200MOE_DEVICE_TIMEOUT to the status word and returns.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "ptx.cuh"
 #include "tma_host.cuh"
@@ -399,7 +401,8 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         c.as_ptr = p.a_s + row_ld * p.a_s_stride;
         c.bs0_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb0) * KB;
         c.bs1_ptr = p.b_s + (static_cast<int64_t>(tl.expert) * NB + nb1) * KB;
-        c.sa = __ldg(c.as_ptr); c.b0 = __ldg(c.bs0_ptr); c.b1 = __ldg(c.bs1_ptr);
+        const int kb0 = tl.ks * KBs;               // first K block of this tile's K split
+        c.sa = __ldg(c.as_ptr + kb0); c.b0 = __ldg(c.bs0_ptr + kb0); c.b1 = __ldg(c.bs1_ptr + kb0);
       }
       return c;
     };
@@ -419,15 +422,17 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
       float acc[128];
 #pragma unroll
       for (int j = 0; j < 128; ++j) acc[j] = 0.f;
-      const int KBp = kPromote ? KB : 1;              // TMEM read-backs per tile
+      // TMEM read-backs of this tile: promoted kinds one per K block of the tile's K split, the others one
+      const int kb0p = kPromote ? tl.ks * KBs : 0;
+      const int kb1p = kPromote ? min(KB, kb0p + KBs) : 1;
       // Per K block: two batches of two 32-column loads.  The second batch is in flight during the
       // FMAs of the first; the first batch of the NEXT K block is issued before the last 64 FMAs of
       // this one whenever its product is already there, so those FMAs hide its latency too.
       uint32_t ra[32], rb[32];
       bool issued = false;                            // first batch of this K block already in flight
-      for (int kb = 0; kb < KBp; ++kb) {
+      for (int kb = kb0p; kb < kb1p; ++kb) {
         const float s0 = sa_n * b0_n, s1 = sa_n * b1_n;
-        if (kPromote && kb + 1 < KB) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
+        if (kPromote && kb + 1 < kb1p) { sa_n = __ldg(as_ptr + kb + 1); b0_n = __ldg(bs0_ptr + kb + 1); b1_n = __ldg(bs1_ptr + kb + 1); }
         const uint32_t tcol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
         if (!issued) {
           // warp-uniform outcome: the TMEM loads below need the whole warp converged
@@ -451,7 +456,7 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         }
         if (++as == kAccStages) { as = 0; aphase ^= 1u; }
         issued = false;
-        if (kb + 1 < KBp && __all_sync(0xffffffffu, ptx::mbar_try_wait(&sh->tmem_full[as], aphase))) {
+        if (kb + 1 < kb1p && __all_sync(0xffffffffu, ptx::mbar_try_wait(&sh->tmem_full[as], aphase))) {
           const uint32_t ncol = tmem_base + lane_base + static_cast<uint32_t>(as) * BN + static_cast<uint32_t>(hsel) * 64;
           ptx::tc_fence_after_sync();
           promote32<KIND>(acc + 64, ra, s1);
@@ -688,6 +693,63 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
                static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr, nullptr, 0};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
+}
+
+namespace b200moe {
+// out[i] = T(partials[0][i] + partials[1][i] + ...) in split order (deterministic), 4 values per thread
+template <typename T>
+__global__ void __launch_bounds__(256) sum_splits_kernel(const float* __restrict__ partials, int ksplits,
+                                                         int64_t n, T* __restrict__ out) {
+  for (int64_t i = (static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 4; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x * 4) {
+    float4 acc = *reinterpret_cast<const float4*>(partials + i);
+    for (int s = 1; s < ksplits; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(partials + s * n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if constexpr (sizeof(T) == 4) {
+      *reinterpret_cast<float4*>(out + i) = acc;
+    } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(out + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else {
+      __half2 lo = __floats2half2_rn(acc.x, acc.y), hi = __floats2half2_rn(acc.z, acc.w);
+      *reinterpret_cast<uint2*>(out + i) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    }
+  }
+}
+}  // namespace b200moe
+
+extern "C" int b200moe_gemm_fp8_block_splitk(const void* a, const float* a_s, const void* b, const float* b_s,
+                                             void* c, int c_dtype, int64_t M, int64_t N, int64_t K, int ksplits,
+                                             float* partials, int64_t partials_bytes, void* stream) {
+  B200MOE_REQUIRE(a && a_s && b && b_s && c && partials, B200MOE_BAD_ARG, "gemm_fp8_block_splitk: null pointer");
+  B200MOE_REQUIRE(M >= 0 && M < (int64_t(1) << 31) && N > 0 && K > 0 && K % 128 == 0 && N % 128 == 0 && N * K < (int64_t(1) << 40),
+                  B200MOE_BAD_SHAPE, "gemm_fp8_block_splitk: M=%lld N=%lld K=%lld (N and K must be multiples of 128)",
+                  (long long)M, (long long)N, (long long)K);
+  const int64_t KB = K / 128;
+  const int64_t per = ksplits > 0 ? (KB + ksplits - 1) / ksplits : 0;
+  B200MOE_REQUIRE(ksplits >= 1 && ksplits <= 16 && per * (ksplits - 1) < KB, B200MOE_BAD_ARG,
+                  "gemm_fp8_block_splitk: %d splits of %lld K blocks (every split needs at least one)", ksplits, (long long)KB);
+  B200MOE_REQUIRE(c_dtype == B200MOE_F32 || c_dtype == B200MOE_F16 || c_dtype == B200MOE_BF16, B200MOE_BAD_DTYPE,
+                  "gemm_fp8_block_splitk: c dtype %d", c_dtype);
+  B200MOE_REQUIRE(aligned(a, 16) && aligned(b, 16) && aligned(c, 16) && aligned(partials, 16), B200MOE_BAD_ALIGN,
+                  "gemm_fp8_block_splitk: Input tensors must be 16-byte aligned");
+  B200MOE_REQUIRE(partials_bytes >= static_cast<int64_t>(ksplits) * M * N * 4, B200MOE_WORKSPACE_TOO_SMALL,
+                  "gemm_fp8_block_splitk: partials need %lld bytes", (long long)(static_cast<int64_t>(ksplits) * M * N * 4));
+  if (M == 0) return B200MOE_OK;
+  GemmParams p{a_s, K / 128, b_s, partials, N * 4, nullptr, 0, nullptr, nullptr, M,
+               static_cast<int>(N), static_cast<int>(K), 1, 1, B200MOE_F32, 0, nullptr, ksplits, M * N * 4, 0,
+               nullptr, nullptr, 0};
+  const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * ksplits;
+  if (int rc = launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream))) return rc;
+  const int64_t n = M * N;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((n / 4 + 255) / 256, 148 * 8));
+  cudaStream_t st = as_stream(stream);
+  if (c_dtype == B200MOE_F32) sum_splits_kernel<float><<<grid, 256, 0, st>>>(partials, ksplits, n, static_cast<float*>(c));
+  else if (c_dtype == B200MOE_BF16) sum_splits_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(partials, ksplits, n, static_cast<__nv_bfloat16*>(c));
+  else sum_splits_kernel<__half><<<grid, 256, 0, st>>>(partials, ksplits, n, static_cast<__half*>(c));
+  return check_launch("sum_splits");
 }
 
 extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_bytes, const float* a_s,

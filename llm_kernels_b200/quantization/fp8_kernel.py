@@ -52,10 +52,27 @@ def weight_dequant(x: torch.Tensor, s: torch.Tensor, block_size: int = 128) -> t
     return y
 
 
+_partials = {}
+
+
+def _split_k(M: int, Nn: int, K: int) -> int:
+    """K splits for a small-M product: enough tiles to occupy the 148 SMs, every split non-empty."""
+    if M > 128:
+        return 1
+    tiles = -(-M // 128) * -(-Nn // 256)
+    kb = K // 128
+    ks = max(1, min(8, 148 // tiles, kb))
+    while ks > 1 and -(-kb // ks) * (ks - 1) >= kb:
+        ks -= 1
+    return ks
+
+
 def fp8_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor,
-             out_dtype: torch.dtype = None) -> torch.Tensor:
+             out_dtype: torch.dtype = None, ksplits: int = None) -> torch.Tensor:
     """c[..., N] = a[..., K] . b[N, K]^T with 1x128 / 128x128 f32 block scales, in the
-    default dtype unless out_dtype is given (tcgen05 kernel)."""
+    default dtype unless out_dtype is given (tcgen05 kernel).  ksplits (None = chosen from the shape):
+    M <= 128 splits the K loop over several sets of tiles whose f32 partial products are added in
+    split order by a second kernel, so that the weights stream on all SMs."""
     N.require_cuda(a, a_s, b, b_s)
     assert a.is_contiguous() and b.is_contiguous(), 'Input tensors must be contiguous'
     assert a_s.is_contiguous() and b_s.is_contiguous(), 'Scaling factor tensors must be contiguous'
@@ -65,6 +82,16 @@ def fp8_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Ten
     M = a.numel() // K
     Nn = b.size(0)
     c = a.new_empty(*a.size()[:-1], Nn, dtype=out_dtype or torch.get_default_dtype())
+    ks = _split_k(M, Nn, K) if ksplits is None else int(ksplits)
+    if ks > 1 and M > 0:
+        key = (a.device, torch.cuda.current_stream(a.device).cuda_stream)
+        part = _partials.get(key)
+        if part is None or part.numel() < ks * M * Nn:
+            part = _partials[key] = torch.empty(ks * M * Nn, dtype=torch.float32, device=a.device)
+        N.check(N.lib().b200moe_gemm_fp8_block_splitk(N.ptr(a), N.ptr(a_s), N.ptr(b), N.ptr(b_s), N.ptr(c),
+                                                      N.dtype_code(c.dtype), M, Nn, K, ks, N.ptr(part),
+                                                      part.numel() * 4, N.stream()))
+        return c
     N.check(N.lib().b200moe_gemm_fp8_block(N.ptr(a), N.ptr(a_s), N.ptr(b), N.ptr(b_s), N.ptr(c),
                                            N.dtype_code(c.dtype), M, Nn, K, N.stream()))
     return c

@@ -280,6 +280,25 @@ def test_fp8_gemm_dense(dev, M, N, K, out_dtype):
     torch.testing.assert_close(c.cpu().float(), ref, rtol=2e-2, atol=2e-2 * float(ref.abs().max()))
 
 
+@pytest.mark.parametrize("M,N,K,ks", [(16, 512, 2048, 8), (128, 1024, 7168, 5), (100, 256, 1024, 3)])
+def test_fp8_gemm_split_k(dev, M, N, K, ks):
+    """Small-M products split the K loop over several sets of tiles (f32 partials added in split order):
+    same result as the unsplit kernel up to f32 summation order."""
+    from llm_kernels_b200.quantization import fp8_kernel
+    aq, a_s, bq, b_s = _quant_ab(M, N, K, 3)
+    d = [x.to(dev) for x in (aq, a_s, bq, b_s)]
+    one = fp8_kernel.fp8_gemm(*d, out_dtype=torch.float32, ksplits=1)
+    split = fp8_kernel.fp8_gemm(*d, out_dtype=torch.float32, ksplits=ks)
+    auto = fp8_kernel.fp8_gemm(*d, out_dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    ref = R.fp8_gemm(aq, a_s, bq, b_s, out_dtype=torch.float32)
+    assert R.rel_fro(split.cpu(), one.cpu()) < 1e-6
+    assert R.rel_fro(split.cpu(), ref) < 1e-5
+    assert R.rel_fro(auto.cpu().float(), ref) < 3e-3
+    with pytest.raises(AssertionError):
+        fp8_kernel.fp8_gemm(*d, out_dtype=torch.float32, ksplits=K // 128 + 1)     # an empty split
+
+
 @pytest.mark.parametrize("out_dtype", [torch.float32, torch.float16])
 def test_fp8_gemm_dense_out_dtypes(dev, out_dtype):
     from llm_kernels_b200.quantization import fp8_kernel
