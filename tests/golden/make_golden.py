@@ -120,6 +120,30 @@ def main():
         y_s = model_s(x)
     put("moe_dense_shared", shared_gate_w=sg, shared_up_w=su, shared_down_w=sd, y=y_s.view(-1, 64))
 
+    # ---------------- EPMoE.forward, one rank, fp16, unquantized ---------------------------
+    # (moe/sglang_moe_all_gather_all_reduce.py:267-446: gate -> run_moe_ep_preproess -> pre_reorder ->
+    #  grouped GEMM -> silu_and_mul -> grouped GEMM -> post_reorder, its Triton kernels interpreted)
+    import sglang_moe_all_gather_all_reduce as ref_ep
+    cfg_e = Config()
+    cfg_e.hidden_size, cfg_e.moe_intermediate_size = 64, 32
+    cfg_e.n_routed_experts, cfg_e.num_experts_per_tok = 8, 2
+    cfg_e.n_group, cfg_e.topk_group, cfg_e.routed_scaling_factor = 1, 1, 1.0
+    cfg_e.n_shared_experts, cfg_e.ep_size = None, 1
+    cfg_e.quantize_method, cfg_e.use_block_quant = None, False
+    torch.set_default_dtype(torch.float16)
+    epmoe = ref_ep.EPMoE(cfg_e).eval()
+    torch.set_default_dtype(torch.float32)
+    ge = torch.Generator().manual_seed(31)
+    with torch.no_grad():
+        epmoe.gate.weight.copy_(torch.randn(8, 64, generator=ge) * 0.3)
+        epmoe.w13_weight.copy_((torch.randn(8, 64, 64, generator=ge) * 0.1).half())
+        epmoe.w2_weight.copy_((torch.randn(8, 64, 32, generator=ge) * 0.1).half())
+        xe = torch.randn(1, 24, 64, generator=ge).half()
+        ie, we = epmoe.gate(xe)
+        ye = epmoe(xe)
+    put("epmoe_fp16", x=xe[0], gate_W=epmoe.gate.weight.detach(), w13=epmoe.w13_weight.detach(),
+        w2=epmoe.w2_weight.detach(), topk_idx=ie, topk_weight=we, y=ye[0])
+
     # ---------------- run_moe_ep_preproess (moe/group_gemm_kernel.py:48-78) -----------
     for case, (T, k, E, seed) in {"prep_small": (6, 2, 4, 31), "prep_skew": (200, 8, 64, 32),
                                   "prep_empty_experts": (33, 2, 32, 33)}.items():

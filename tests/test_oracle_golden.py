@@ -50,6 +50,27 @@ def test_moe_dense_with_shared_experts_matches_reference(golden):
     torch.testing.assert_close(y, t(cs["y"]), rtol=1e-5, atol=1e-6)
 
 
+def test_epmoe_forward_matches_reference(golden):
+    """EPMoE.forward on one rank, fp16, unquantized (moe/sglang_moe_all_gather_all_reduce.py:267-446, its
+    Triton kernels run by the interpreter): the restated stages chained the same way reproduce it."""
+    c = golden.case("epmoe_fp16")
+    x = t(c["x"], torch.float16)
+    w13, w2 = t(c["w13"], torch.float16), t(c["w2"], torch.float16)
+    ids, w = t(c["topk_idx"]), t(c["topk_weight"])
+    gi, gw = R.gate_forward(x, t(c["gate_W"]), None, top_k=2, n_group=1, topk_group=1,
+                            scoring_func="sigmoid", routed_scaling_factor=1.0)
+    assert torch.equal(R.canonical_rows(gi, gw)[0], R.canonical_rows(ids, w)[0])
+    E, T, k = w13.shape[0], x.shape[0], ids.shape[1]
+    reorder_ids, src2dst, seg = R.run_moe_ep_preproess(ids, E)
+    a1 = R.pre_reorder(x, src2dst, ids, None, 0, E - 1, torch.zeros(T * k, x.shape[1], dtype=torch.float16))
+    widx = torch.arange(E)
+    gu = R.grouped_gemm_plain(a1, w13, seg, widx)
+    h = R.silu_and_mul(gu, reorder_ids, None, 0, E - 1, torch.zeros(T * k, w13.shape[1] // 2, dtype=torch.float16))
+    down = R.grouped_gemm_plain(h, w2, seg, widx)
+    y = R.post_reorder(down, src2dst, ids, w, 0, E - 1)
+    torch.testing.assert_close(y, t(c["y"], torch.float16), rtol=4e-3, atol=4e-4)
+
+
 @pytest.mark.parametrize("case", ["prep_small", "prep_skew", "prep_empty_experts"])
 def test_preprocess_bit_exact(golden, case):
     c = golden.case(case)
