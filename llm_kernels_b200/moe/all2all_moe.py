@@ -7,11 +7,16 @@ its fused path as a stub (``triton_group_gemm_moe_infer``, :282-286), this modul
 one fused pipeline of sm_100a kernels:
 
     router_topk -> route_metadata -> permute + 1x128 e4m3 quantize
-      -> [all-to-all-v dispatch of fp8 rows + scales, one packed record per row]
+      -> [dispatch of fp8 rows + scales, one packed record per row]
       -> grouped GEMM-1 (tcgen05) with SwiGLU + re-quantize in the epilogue
       -> grouped GEMM-2 (tcgen05)
-      -> [all-to-all-v combine, bf16 rows]
+      -> [return of bf16 rows to their source ranks]
       -> routing-weighted un-permute (f32 accumulate)
+
+With expert parallelism the two bracketed steps are, by default, part of the kernels next to them
+(config.ep_exchange = "fused": the permute kernel copies each record into its owner's peer-mapped
+buffer and the second GEMM stores each output row into its source rank's buffer, both over NVLink);
+"nccl" runs them as all_to_all_single calls like the reference, "push" as copy-engine peer copies.
 
 Experts are sharded as in the reference (:130-147): rank r owns experts
 [r*E/ep, (r+1)*E/ep).  Expert weights live in the fused layout of the reference's
