@@ -14,10 +14,16 @@ public layer call with HOST buffers: the pinned host->device copy of the step's 
 the device->host read of its output are inside the timed region, on copy streams of their own
 so that they overlap the neighbouring steps' compute as in a serving loop.  `roofline` describes the
 dominant kernel (the gate/up grouped GEMM), `cpu_baseline` times the CPU restatement of the
-reference's torch path on the host cores on a bounded sample.
+reference's torch path on the host cores on a bounded sample.  `parity` is a reduced-shape forward
+through the same expert-parallel exchange the timed run uses, every rank checked against the CPU
+oracle before anything is timed (the run fails above the tolerance).  At N = 1 `configs` adds
+device-timed records of the other benchmark configurations (dense fp8 GEMM shapes, the w4a16
+and w4a8 layers).
 
---impl reference times that CPU path alone (the reference is Python + Triton and has no
-installable CPU build; its torch code path is what oracle/restate.py restates).
+--impl reference times the CPU path alone: the reference is a set of Python scripts that exists
+only on the development machine, so what runs here is oracle/restate.py's restatement of its
+torch code path (MoEGate + the per-expert loop of moe_infer), every step over the full 4096-token
+batch.
 """
 import argparse
 import json
@@ -65,7 +71,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50"],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -178,16 +184,18 @@ def run_reference(args):
     from llm_kernels_b200 import workloads as WL
     shape = WL.CONFIG3 if args.shape == "cfg3" else WL.CONFIG3_SMALL
     t0 = time.perf_counter()
-    v, cores, sample = cpu_reference_run(shape, lambda: cpu_weights_random(shape), args.cpu_tokens, args.steps,
-                                         args.warmup, budget_s=150.0)
+    # every step is one pass over the full batch of the workload (a fixed sample: the whole 4096 tokens)
+    v, cores, sample = cpu_reference_run(shape, lambda: cpu_weights_random(shape), shape.tokens, args.steps,
+                                         args.warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * sample / v,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "config": _config(shape, args.gpus),
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} of {shape.tokens} tokens per step, all {shape.experts} experts, bf16 "
-                                   f"weights, torch CPU per-expert loop ({time.perf_counter() - t0:.0f} s incl. setup)"},
+                         "sample": f"{sample} of {shape.tokens} tokens per step (fixed), all {shape.experts} experts, bf16 "
+                                   f"weights, torch CPU per-expert loop, median of {args.steps} steps after "
+                                   f"{args.warmup} ({time.perf_counter() - t0:.0f} s incl. setup)"},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -203,24 +211,164 @@ def _config(shape, n):
 
 
 # ------------------------------------------------------------------------------------------
+def bind_to_gpu_numa_node(dev):
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off, so that the pinned host buffers
+    allocated afterwards are node-local (first touch) and N ranks' host<->device copies do not all land
+    on one socket's memory.  Returns a short description, or None when the topology cannot be read."""
+    try:
+        props = torch.cuda.get_device_properties(dev)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
+        if node < 0:
+            return None
+        cpus = set()
+        for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return f"node{node}:{len(allowed)}cpus"
+    except Exception:
+        return None
+
+
+def parity_check(world, rank, dev, exchange):
+    """One reduced-shape forward (32 experts top-4 of 2 of 4 groups, hidden 512, SwiGLU 256, 96 + 32 r tokens on
+    rank r) through the exchange the timed run uses; every rank compares with the CPU oracle, which does not
+    depend on the EP degree.  Returns the dict for the JSON line (max / all over ranks)."""
+    import torch.distributed as dist
+    from dataclasses import replace
+    from llm_kernels_b200 import workloads as WL
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+    from oracle import restate as R
+    shape = replace(WL.CONFIG3, tokens=96 + 32 * rank, hidden=512, inter=256, experts=32, n_group=4, topk_group=2,
+                    top_k=4)
+    cfg = WL.make_config(shape, ep_size=world)
+    cfg.ep_exchange = exchange
+    layer = DeepseekV3MoE(cfg, device=dev).eval()
+    WL.fill_layer_cpu_seeded(layer, shape)
+    x = WL.tokens(shape, rank=rank)
+    xd = x.to(dev).view(1, shape.tokens, -1)
+    layer(xd)
+    y = layer(xd)                                   # second pass: buffers and peer mappings are re-used
+    gi, gw = layer.gate(xd)
+    layer.check_status()
+    W, bias = WL.router_params(shape)
+    kw = dict(top_k=shape.top_k, n_group=shape.n_group, topk_group=shape.topk_group, scoring_func=shape.scoring)
+    ok = R.gate_margins_fp64(x, W, bias, **kw) > 1e-5
+    idx, w = R.gate_forward(x, W, bias, routed_scaling_factor=shape.scaling, **kw)
+    routing = bool(torch.equal(R.canonical_rows(gi.cpu(), gw.cpu())[0][ok], R.canonical_rows(idx, w)[0][ok]))
+    q13, q2 = [], []
+    for e in range(shape.experts):
+        g, u, d = WL.expert_weights_cpu(shape, e)
+        q13.append(R.weight_quant_fp8(torch.cat([g, u], 0)))
+        q2.append(R.weight_quant_fp8(d))
+    y_ref = R.moe_layer_fp8(x, idx, w, torch.stack([a for a, _ in q13]), torch.stack([s for _, s in q13]),
+                            torch.stack([a for a, _ in q2]), torch.stack([s for _, s in q2]), ep_size=world)
+    err = R.rel_fro(y.cpu().view(shape.tokens, -1).float(), y_ref.float())
+    stat = torch.tensor([err, 0.0 if routing else 1.0], device=dev, dtype=torch.float64)
+    rows = torch.tensor([layer.last_recv_rows, shape.tokens * shape.top_k], device=dev)
+    if world > 1:
+        dist.all_reduce(stat, op=dist.ReduceOp.MAX)
+        dist.all_reduce(rows)
+    del layer
+    return {"rel_fro_max": float(stat[0]), "tolerance": 1e-2, "routing_exact": float(stat[1]) == 0.0,
+            "rows_conserved": int(rows[0]) == int(rows[1]), "ep": world, "exchange": exchange,
+            "case": "32 experts top-4 (groups 4/2), hidden 512, SwiGLU 256, 96 + 32*rank tokens per rank, "
+                    "checked against the CPU oracle on every rank"}
+
+
+def _time_launches(fn, n, dev):
+    """Average device time (ms) of n back-to-back calls of fn(i), CUDA events on the current stream."""
+    fn(0)
+    torch.cuda.synchronize(dev)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for i in range(n):
+        fn(i)
+    e.record()
+    e.synchronize()
+    return s.elapsed_time(e) / n
+
+
+def other_configs(dev, peaks, fp8_peak):
+    """Device-timed records of the benchmark configurations that are not the headline (N = 1 only).
+    cfg1: dense fp8 blockwise GEMM N = K = 7168, M in {16, 128, 1024, 4096}; the weight rotates over
+    4 copies (205 MB > L2) so every launch streams it from HBM; 20 back-to-back launches.
+    cfg2: w4a16 layer at full width (8 experts, H 4096, I 14336, 8192 tokens = the 16384 rows one rank's expert
+    processes at EP = 8).  cfg4: w4a8 layer, 64 tokens, 256 experts."""
+    from llm_kernels_b200 import workloads as WL
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+    from llm_kernels_b200.quantization import fp8_kernel
+    out = {}
+    tensor_peak = fp8_peak or 2 * peaks["bf16_tflops"]
+    N_, K = 7168, 7168
+    g = torch.Generator(device=dev).manual_seed(1)
+    bq, b_s = fp8_kernel.weight_quant(torch.randn(N_, K, generator=g, device=dev) * 0.02)
+    bqs = [bq.clone() for _ in range(4)]
+    cfg1 = {}
+    for M in (16, 128, 1024, 4096):
+        aq, a_s = fp8_kernel.act_quant(torch.randn(M, K, generator=g, device=dev).to(torch.bfloat16))
+        ms = _time_launches(lambda i: fp8_kernel.fp8_gemm(aq, a_s, bqs[i & 3], b_s, out_dtype=torch.bfloat16), 20, dev)
+        tf = 2.0 * M * N_ * K / (ms * 1e-3) / 1e12
+        gbs = (N_ * K + M * K + 2 * M * N_ + 4 * (N_ // 128) * (K // 128) + 4 * M * (K // 128)) / (ms * 1e-3) / 1e9
+        cfg1[str(M)] = {"us": ms * 1e3, "tflops": tf, "frac_of_fp8_burst_peak": tf / tensor_peak, "gbs": gbs,
+                        "frac_of_hbm_peak": gbs / peaks["hbm_gbs"]}
+    out["cfg1_dense_fp8_gemm_n7168_k7168"] = cfg1
+    del bqs, bq
+    for name, shape in (("cfg2_w4a16_mixtral_8192tok", WL.CONFIG2), ("cfg4_w4a8_decode_64tok", WL.CONFIG4)):
+        layer = DeepseekV3MoE(WL.make_config(shape), device=dev).eval()
+        WL.fill_layer_gpu(layer, shape)
+        x = WL.tokens(shape, device=dev).view(1, shape.tokens, -1)
+        for _ in range(2):
+            layer(x)
+        layer.check_status()
+        ms = _time_launches(lambda i: layer(x), 10, dev)
+        rows = shape.tokens * shape.top_k
+        rec = {"ms_per_step": ms, "tokens_per_s": shape.tokens / (ms * 1e-3),
+               "gemm_tflops_whole_step": 6.0 * shape.hidden * shape.inter * rows / (ms * 1e-3) / 1e12}
+        wbytes = shape.experts * 3 * shape.hidden * shape.inter // 2          # packed int4
+        rec["packed_weight_gbs_whole_step"] = wbytes / (ms * 1e-3) / 1e9
+        if shape.method == "w4a16":
+            rec["frac_of_bf16_peak_whole_step"] = rec["gemm_tflops_whole_step"] / peaks["bf16_tflops"]
+        else:
+            rec["frac_of_hbm_peak_whole_step"] = rec["packed_weight_gbs_whole_step"] / peaks["hbm_gbs"]
+        out[name] = rec
+        del layer
+        torch.cuda.empty_cache()
+    return out
+
+
 def measure_fp8_peak(dev):
-    """Dense e4m3 GEMM 8192^3 through torch._scaled_mm (cuBLASLt), best of 10, TFLOP/s."""
+    """Dense e4m3 GEMM 8192^3 through torch._scaled_mm (cuBLASLt), TFLOP/s: (burst, sustained).  burst = best of
+    12 single launches (the figure for a kernel timed alone); sustained = back-to-back launches for about one
+    second under the power cap (the figure for a kernel timed inside a long loop, as the expert GEMMs are)."""
     try:
         n = 8192
         a = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
         b = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
         one = torch.ones((), device=dev)
+        run = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
         best = None
         for _ in range(12):
             s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             s.record()
-            torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            run()
             e.record(); e.synchronize()
             ms = s.elapsed_time(e)
             best = ms if best is None else min(best, ms)
-        return 2.0 * n ** 3 / (best * 1e-3) / 1e12
+        reps = max(20, int(1000.0 / best))
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(reps):
+            run()
+        e.record(); e.synchronize()
+        flops = 2.0 * n ** 3
+        return flops / (best * 1e-3) / 1e12, flops * reps / (s.elapsed_time(e) * 1e-3) / 1e12
     except Exception:
-        return None
+        return None, None
 
 
 def run_ours(args):
@@ -240,6 +388,7 @@ def run_ours(args):
     os.dup2(2, 1)
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
+    numa = bind_to_gpu_numa_node(dev)          # before any pinned host allocation
     shape = WL.CONFIG3 if args.shape == "cfg3" else WL.CONFIG3_SMALL
     T, H, k = shape.tokens, shape.hidden, shape.top_k
 
@@ -303,19 +452,43 @@ def run_ours(args):
     def e2e_drain():
         s_out.synchronize()                                 # the caller holds every result
 
+    # parity first: a reduced-shape forward through the same exchange, every rank against the CPU oracle
+    parity = parity_check(world, rank, dev, layer.exchange if world > 1 else "none") if args.parity else None
+
     for i in range(args.warmup):
         step(i)
     layer.check_status()
     sampler = ClockSampler("GPU-" + str(torch.cuda.get_device_properties(dev).uuid))
     sampler.start()
-    time.sleep(0.3)
-    ms = timed(step, args.steps)
-    clocks = sampler.stop()
+    time.sleep(1.0)
+    # the timed region (exactly `steps` steps between barriers) is taken `repeats` times back to back so that
+    # the clock sampler sees load for long enough; the median region is reported, all of them are listed
+    regions = [timed(step, args.steps) for _ in range(args.repeats)]
+    ms = statistics.median(regions)
     layer.check_status()
     for i in range(min(args.warmup, 3)):
         step_e2e(i)
     e2e_drain()
-    ms_e2e = timed(step_e2e, args.steps, drain=e2e_drain)
+    regions_e2e = [timed(step_e2e, args.steps, drain=e2e_drain) for _ in range(args.repeats)]
+    ms_e2e = statistics.median(regions_e2e)
+    clocks = sampler.stop()
+
+    # ceiling of the host<->device traffic alone: every rank copies one step's input in and one step's output
+    # out at the same time, no compute
+    dev_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
+
+    def copy_only(i):
+        b = i & 1
+        with torch.cuda.stream(s_in):
+            dev_ins[b].copy_(host_in[i % nbatch], non_blocking=True)
+        with torch.cuda.stream(s_out):
+            host_outs[b].copy_(dev_out, non_blocking=True)
+
+    def copy_drain():
+        torch.cuda.current_stream().wait_stream(s_in)
+        torch.cuda.current_stream().wait_stream(s_out)
+
+    ms_copy = timed(copy_only, args.steps, drain=copy_drain)
 
     # per-stage device times (separate pass, events between the stages)
     layer.stage_events = []
@@ -355,8 +528,9 @@ def run_ours(args):
         else:               # with the exchange in between the in-step events include waits: use the re-launches
             g1_s, g2_s = g1_ms * 1e-3, g2_ms * 1e-3
         hbm_bound = world == 1
-        fp8_peak = measure_fp8_peak(dev) if args.fp8_peak else None
-        tensor_peak = fp8_peak or 2 * peaks["bf16_tflops"]
+        fp8_peak, fp8_sustained = measure_fp8_peak(dev) if args.fp8_peak else (None, None)
+        # the expert GEMMs are timed inside loops of tens of milliseconds: the sustained figure is their peak
+        tensor_peak = fp8_sustained or 2 * peaks["bf16_tflops_sustained"]
         if hbm_bound:
             ach = g1_bytes / g1_s / 1e9
             roof = {"kernel": "gemm_block_kernel<fp8> (gate/up + SwiGLU epilogue)", "bound": "hbm", "achieved": ach,
@@ -371,15 +545,21 @@ def run_ours(args):
             ach = g1_flops / g1_s / 1e12
             roof = {"kernel": "gemm_block_kernel<fp8> (gate/up + SwiGLU epilogue)", "bound": "tensor", "achieved": ach,
                     "peak": tensor_peak, "unit": "TFLOP/s", "frac": ach / tensor_peak, "traffic": None,
-                    "peak_source": "torch._scaled_mm e4m3 8192^3 measured in this run" if fp8_peak else
-                                   f"2 x {peaks['source']} bf16 cuBLAS", "algorithmic_flops": g1_flops}
+                    "peak_source": "torch._scaled_mm e4m3 8192^3 back to back for 1 s in this run (sustained; the "
+                                   "kernel is timed in a loop of the same kind)" if fp8_sustained else
+                                   f"2 x {peaks['source']} sustained bf16 cuBLAS",
+                    "frac_of_burst_peak": ach / fp8_peak if fp8_peak else None,
+                    "frac_of_nominal_fp8_4500": ach / NOMINAL_FP8_TFLOPS, "algorithmic_flops": g1_flops}
         line = {
             "metric": METRIC, "value": tokens_per_s, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "fp8_e4m3", "data": "synthetic", "config": _config(shape, world),
             "clocks": clocks,
             "e2e": {"value": e2e_tokens_per_s, "unit": UNIT, "h2d_bytes_per_step": T * H * 2,
-                    "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e / args.steps},
+                    "d2h_bytes_per_step": T * H * 2, "ms_per_step": ms_e2e / args.steps,
+                    "ms_per_step_all": [r / args.steps for r in regions_e2e],
+                    "copy_only_ms_per_step": ms_copy / args.steps, "host_numa_binding": numa},
+            "repeats": args.repeats, "ms_per_step_all": [r / args.steps for r in regions],
             # this library's kernels per step: router GEMM + selection, 3 of the counting sort, permute,
             # un-permute (7); then 2 grouped GEMMs per pass (+ 1 row gather per pass behind the NCCL and
             # copy-engine exchanges), or 2 plan kernels + 2 grouped GEMMs for the fused exchange
@@ -390,8 +570,10 @@ def run_ours(args):
             "grouped_gemm": {"gemm1_tflops": g1_flops / g1_s / 1e12, "gemm2_tflops": g2_flops / g2_s / 1e12,
                              "both_tflops": (g1_flops + g2_flops) / (g1_s + g2_s) / 1e12,
                              "frac_of_nominal_fp8_4500": (g1_flops + g2_flops) / (g1_s + g2_s) / 1e12 / NOMINAL_FP8_TFLOPS,
-                             "fp8_peak_measured_tflops": fp8_peak},
+                             "fp8_peak_measured_tflops": fp8_peak, "fp8_peak_sustained_tflops": fp8_sustained},
         }
+        if parity is not None:
+            line["parity"] = parity
         if world == 1 and args.cpu_tokens > 0:
             t0 = time.perf_counter()
             v, cores, _ = cpu_reference_run(shape, lambda: cpu_weights_from_layer(layer, shape), args.cpu_tokens, 2, 1)
@@ -400,12 +582,22 @@ def run_ours(args):
                 "sample": f"{args.cpu_tokens} of {T} tokens, all {shape.experts} experts (dequantized bf16 copies of the "
                           f"same weights), torch CPU per-expert loop, median of 2 after 1 warm-up "
                           f"({time.perf_counter() - t0:.0f} s incl. setup)"}
+        if world == 1 and args.configs:
+            xs.clear(); dev_ins.clear()
+            layer._buffers_cache.clear()
+            layer.to_empty(device="cpu")                   # frees the 11 GB of expert weights on the device
+            torch.cuda.empty_cache()
+            line["configs"] = other_configs(dev, peaks, fp8_peak)
         sys.stdout.flush()
         os.write(json_fd, (json.dumps(line) + "\n").encode())
     os.close(json_fd)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if parity is not None and not (parity["rel_fro_max"] < parity["tolerance"] and parity["routing_exact"]
+                                   and parity["rows_conserved"]):
+        sys.stderr.write(f"parity check failed: {parity}\n")
+        sys.exit(3)
 
 
 def main():
@@ -426,6 +618,10 @@ def main():
                     help="GEMM grid cap while NCCL kernels overlap (N > 1, passes > 1); 0 = all SMs")
     ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens in the CPU baseline sample (0 = skip)")
     ap.add_argument("--no-fp8-peak", dest="fp8_peak", action="store_false")
+    ap.add_argument("--no-parity", dest="parity", action="store_false", help="skip the reduced-shape parity pass")
+    ap.add_argument("--no-configs", dest="configs", action="store_false",
+                    help="skip the records of the other benchmark configurations (N = 1)")
+    ap.add_argument("--repeats", type=int, default=5, help="timed regions of `steps` steps; the median is reported")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -104,6 +104,18 @@ B200MOE_API int b200moe_gemm_fp8_block_splitk(const void* a, const float* a_s, c
 B200MOE_API int b200moe_act_quant_int8(const void* x, int x_dtype, int64_t rows, int64_t cols,
                            void* y, void* s_f16, int rounding, void* stream);
 
+/* weight_quant (quantization/int8_kernel.py:59-113): per 128x128 block s = amax/qmax stored as
+ * f16 [ceil(M/128), ceil(N/128)], y int8 [M,N] = round(w / s) with the f32 scale.
+ * qmax 127, rounding 0 (half away from zero, unclamped) is int8_kernel.weight_quant;
+ * qmax 119, rounding 1 (floor(v + 0.5) clamped to +-qmax) is the first level of the two-level
+ * int4 quantizer (weight_quant_int8_kernel, quantization/w4a8_kernel.py:196-225). */
+B200MOE_API int b200moe_weight_quant_int8(const void* w, int w_dtype, void* y_int8, void* s_f16,
+                              int64_t M, int64_t N, float qmax, int rounding, void* stream);
+
+/* weight_dequant (quantization/int8_kernel.py:116-170): y = float(x) * s[i/128, j/128]. */
+B200MOE_API int b200moe_weight_dequant_int8(const void* x_int8, const void* s_f16, void* y, int y_dtype,
+                                int64_t M, int64_t N, void* stream);
+
 /* ========================= moe/all2all_moe.py ============================= */
 
 /* MoEGate.forward (moe/all2all_moe.py:60-118).
@@ -248,6 +260,7 @@ B200MOE_API int b200moe_post_reorder(const void* down_output, int dtype, void* o
  *   [M_total, N/2] with row stride c_row_stride_bytes and c_s f32
  *   [M_total, N/2/128] with row stride c_s_row_stride.  Intermediates are
  *   rounded to bf16 where the reference rounds to its activation dtype.
+ * epilogue 4: as 1 with the tanh-GELU of gelu_and_mul_triton_kernel (:176-235) in place of SiLU.
  * c_row_map (epilogue 0 only, may be NULL): int32 [M_total]; output row r is stored at row
  * c_row_map[r], which un-does a row gather in the store instead of in a separate pass.
  * c_row_addr (epilogue 0 only, may be NULL, exclusive with c_row_map): int64 [M_total]; output row
@@ -255,7 +268,7 @@ B200MOE_API int b200moe_post_reorder(const void* down_output, int dtype, void* o
  * another GPU's memory: the expert-parallel return trip (the second all_to_all_single of
  * moe/all2all_moe.py:248-262) then happens in the stores of the down projection.
  * Rows outside every group are not written.  K % 128 == 0, N % 128 == 0
- * (epilogue 1: N % 256 == 0).  status_word (may be NULL): a device int32 that
+ * (epilogues 1 and 4: N % 256 == 0).  status_word (may be NULL): a device int32 that
  * receives B200MOE_DEVICE_TIMEOUT if a bounded wait inside the kernel expires. */
 B200MOE_API int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_bytes,
                              const float* a_s, int64_t a_s_row_stride,
@@ -300,6 +313,23 @@ B200MOE_API int b200moe_w4a8_expand_int8(const void* packed, const int8_t* s4, c
 B200MOE_API int b200moe_w4a16_expand_bf16(const void* packed, const void* scale_bf16, const void* zero_bf16,
                               void* out_bf16, int64_t rows, int64_t K, void* stream);
 
+/* weight_quant of the two-level format in one kernel (quantization/w4a8_kernel.py:196-309):
+ * level 1 per 128x128 block s = amax/119 (f16 out), y8 = clamp(floor(w/s + 0.5), +-119);
+ * level 2 per (row, 128 columns): s4 = floor((max - min)/15 + 0.5), z4 = floor(-min/s4 + 0.5),
+ * q = clamp(floor(y8/s4 + 0.5) + z4, 0, 15); packed over rows (pack_weights_over_rows,
+ * quantization/bitpack.py:9-36).  w [M,N]; packed int32 [M/8, N]; s f16 [M/128, N/128];
+ * s4, z4 int8 [M, N/128].  M % 128 == 0, N % 128 == 0. */
+B200MOE_API int b200moe_weight_quant_w4a8(const void* w, int w_dtype, void* packed_i32, void* s_f16,
+                              int8_t* s4, int8_t* z4, int64_t M, int64_t N, void* stream);
+
+/* Asymmetric group-128 int4 quantizer, the inverse of b200moe_w4a16_expand_bf16 (extends
+ * QuantUtils.fake_quantize, fast_dequant/simple_marlin/utils.py:98-136, with a zero-point): per
+ * (row, 128 columns) scale = bf16(max((max - min)/15, 1e-8)), zero = bf16(clamp(rint(-min/scale),
+ * 0, 15)), q = clamp(rint(w/scale) + zero, 0, 15), packed over columns (quantization/bitpack.py:38-67).
+ * w [rows, K]; packed int32 [rows, K/8]; scale, zero bf16 [rows, K/128].  K % 128 == 0. */
+B200MOE_API int b200moe_weight_quant_w4a16(const void* w, int w_dtype, void* packed_i32, void* scale_bf16,
+                               void* zero_bf16, int64_t rows, int64_t K, void* stream);
+
 /* Grouped int8 x int8 GEMM with 1x128 / 128x128 f32 scales: the grouped form of
  * w4a8_gemm (quantization/w4a8_kernel.py:317-448) once the weights are int8
  * (b200moe_w4a8_expand_int8): acc += float(dot_kb in s32) * a_s[m,kb] * b_s[n/128,kb].
@@ -318,7 +348,8 @@ B200MOE_API int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_byte
  * (moe/group_gemm_kernel.py:120-168) fused, b rows [0,N/2) gate and [N/2,N) up,
  * c bf16 [M_total, N/2].  epilogue 3: c (f16/bf16) = round(c + round(a . b^T)), the sum formed when
  * a module's output is added to a tensor of the same dtype (shared experts,
- * moe/all2all_moe.py:182-183).  K % 64 == 0, N % 128 == 0 (epilogue 2: N % 256 == 0). */
+ * moe/all2all_moe.py:182-183).  epilogue 5: as 2 with the tanh-GELU of :176-235.
+ * K % 64 == 0, N % 128 == 0 (epilogues 2 and 5: N % 256 == 0). */
 B200MOE_API int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
                               int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                               int64_t K, int num_groups, int num_weights,
@@ -338,13 +369,17 @@ B200MOE_API int b200moe_grouped_gemm_f16(const void* a, int64_t a_row_stride_byt
  * fast_dequant/simple_marlin/utils.py:53-95; dequantization of
  * marlin_w4a16_gemm.cu:44-64: (q - 8) * scale) to f16 in nn.Linear layout.
  * packed int32 [K/16, N*2]; scales f16 [K/groupsize, N] (one row when groupsize == -1) in the
- * permuted order QuantUtils.pack returns; out f16 [N, K].  perm1024 (HOST pointer, int16[1024]):
- * packed position i of a 1024-element block holds element perm1024[i]; scale_perm_inverse
- * (HOST pointer, int8[scale_perm_len], 64 grouped / 32 single): packed scale column of original
- * column n is (n / len) * len + scale_perm_inverse[n % len].  K % 16 == 0, N % 64 == 0. */
+ * permuted order QuantUtils.pack returns; out f16 [N, K].  The weight and scale permutations of
+ * utils.py:20-46 are evaluated inside the kernel (no tables, no state shared between calls).
+ * K % 16 == 0, N % 64 == 0. */
 B200MOE_API int b200moe_marlin_expand_f16(const void* packed, const void* scales_f16, void* out_f16,
-                              int64_t K, int64_t N, int64_t groupsize, const int16_t* perm1024,
-                              const int8_t* scale_perm_inverse, int scale_perm_len, void* stream);
+                              int64_t K, int64_t N, int64_t groupsize, void* stream);
+
+/* QuantUtils.pack (fast_dequant/simple_marlin/utils.py:53-95) on the device: q int32 [K, N] with
+ * values 0..15 -> packed int32 [K/16, N*2]; scales f16 [K/groupsize, N] -> scales_out in the
+ * permuted column order (blocks of 64 columns, or of 32 when groupsize == -1). */
+B200MOE_API int b200moe_marlin_pack(const int32_t* q, void* packed_i32, const void* scales_f16,
+                        void* scales_out_f16, int64_t K, int64_t N, int64_t groupsize, void* stream);
 
 /* ============ expert-parallel exchange folded into the kernels ============= */
 /* Replaces the two all_to_all_single calls and the host-side split lists of
@@ -355,8 +390,10 @@ B200MOE_API int b200moe_marlin_expand_f16(const void* packed, const void* scales
  * recv_base / back_base: int64 [ep_size] device arrays with the address, as mapped in THIS
  * process, of each rank's receive buffer ([cap_rows] records of rec_bytes) and return buffer
  * (rows of back_row_bytes in the owner's sorted slot order).  Outputs, all on the device:
- *   dst_base  int64 [num_experts]  where my first record for expert e goes (0 = dropped: the
- *                                  owner's capacity is exceeded; info[1] is set)
+ *   dst_base  int64 [num_experts]  where my first record for expert e goes (0 = dropped: the block
+ *                                  (expert, source rank) does not fit whole into the owner's buffer;
+ *                                  the owner applies the same rule and computes only the rows before
+ *                                  the first block it rejects; info[1] is set on both sides)
  *   local_seg int64 [E/ep + 1]     group table of my local experts over my receive buffer, rows
  *                                  ordered (expert, source rank)
  *   back_addr int64 [cap_rows]     return address of every row I receive (c_row_addr of the
@@ -374,11 +411,14 @@ B200MOE_API int b200moe_ep_plan(const int64_t* counts_all, int rank, int ep_size
  * expert e, at position d = src2dst[slot] of my sorted order, is stored at
  * dst_base[e] + (d - seg_indptr[e]) * rec_bytes: H e4m3 bytes, then H/128 f32 scales at byte H.
  * The stores may cross NVLink; the kernel ends with a system-scope fence, and the caller orders
- * the owner's reads behind a barrier across ranks. */
+ * the owner's reads behind a barrier across ranks.  back_local (may be NULL): this rank's own return
+ * buffer, rows of back_row_bytes in sorted slot order; the rows of slots whose records were dropped
+ * (dst_base == 0) are cleared, so a later weighted sum adds zeros for them. */
 B200MOE_API int b200moe_permute_quant_fp8_push(const void* x, int x_dtype, const int32_t* src2dst,
                                    const int64_t* topk_ids, const int64_t* seg_indptr,
                                    const int64_t* dst_base, int num_experts, int64_t T, int topk,
-                                   int64_t H, int64_t rec_bytes, void* stream);
+                                   int64_t H, int64_t rec_bytes, void* back_local,
+                                   int64_t back_row_bytes, void* stream);
 
 /* ========================= quantization/bitpack.py ======================== */
 

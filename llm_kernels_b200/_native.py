@@ -49,7 +49,7 @@ SIGNATURES = {
                                       _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p, _p]),
     "b200moe_ep_plan_workspace_bytes": (_i64, [_i, _i]),
     "b200moe_ep_plan": (_i, [_p, _i, _i, _i, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _i64, _p]),
-    "b200moe_permute_quant_fp8_push": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i, _i64, _i64, _p]),
+    "b200moe_permute_quant_fp8_push": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i, _i64, _i64, _p, _i64, _p]),
     "b200moe_gather_rows": (_i, [_p, _p, _p, _i64, _i64, _p]),
     "b200moe_set_gemm_max_ctas": (_i, [_i]),
     "b200moe_set_gemm_pair_mode": (_i, [_i]),
@@ -59,7 +59,12 @@ SIGNATURES = {
                                      _p, _p, _p, _p]),
     "b200moe_grouped_gemm_bf16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p]),
     "b200moe_grouped_gemm_f16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p]),
-    "b200moe_marlin_expand_f16": (_i, [_p, _p, _p, _i64, _i64, _i64, _p, _p, _i, _p]),
+    "b200moe_marlin_expand_f16": (_i, [_p, _p, _p, _i64, _i64, _i64, _p]),
+    "b200moe_marlin_pack": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _p]),
+    "b200moe_weight_quant_int8": (_i, [_p, _i, _p, _p, _i64, _i64, _f, _i, _p]),
+    "b200moe_weight_dequant_int8": (_i, [_p, _p, _p, _i, _i64, _i64, _p]),
+    "b200moe_weight_quant_w4a8": (_i, [_p, _i, _p, _p, _p, _p, _i64, _i64, _p]),
+    "b200moe_weight_quant_w4a16": (_i, [_p, _i, _p, _p, _p, _i64, _i64, _p]),
     "b200moe_pack_bits": (_i, [_p, _p, _i64, _i64, _i, _i, _i, _p]),
     "b200moe_unpack_bits": (_i, [_p, _p, _i64, _i64, _i, _i, _i, _p]),
 }
@@ -120,6 +125,17 @@ def stream() -> int:
 
 
 def require_cuda(*tensors) -> None:
+    """Every tensor must live on the CURRENT CUDA device: the launchers take the current device's stream and
+    the library looks its device up with cudaGetDevice, so a tensor of another GPU would have its pointer
+    dereferenced on the wrong device.  Select the device first (torch.cuda.set_device / torch.cuda.device)."""
+    cur = None
     for t in tensors:
-        if t is not None and not t.is_cuda:
+        if t is None:
+            continue
+        if not t.is_cuda:
             raise RuntimeError("b200moe operators run on CUDA tensors only (no CPU path)")
+        if cur is None:
+            cur = torch.cuda.current_device()
+        if t.device.index != cur:
+            raise RuntimeError(f"tensor on cuda:{t.device.index} but the current device is cuda:{cur}: make the "
+                               "tensor's device current before calling (torch.cuda.set_device or torch.cuda.device)")

@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
-SOURCES = ["api.cu", "quant.cu", "router.cu", "route.cu", "permute.cu", "gemm_fp8.cu", "bitpack.cu", "w4.cu", "ep_fused.cu"]
+SOURCES = ["api.cu", "quant.cu", "router.cu", "route.cu", "permute.cu", "gemm_fp8.cu", "bitpack.cu", "w4.cu", "wquant.cu", "ep_fused.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",
@@ -38,19 +38,18 @@ def needs_build() -> bool:
     return any(os.path.getmtime(d) > t for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, extra_flags=(), out: str = LIB) -> str:
-    """extra_flags/out: development builds (e.g. -DB200MOE_PROFILE into another file)."""
-    if not force and not extra_flags and not needs_build():
+def build(force: bool = False, verbose: bool = False) -> str:
+    if not force and not needs_build():
         return LIB
     nvcc = _nvcc()
     objs = []
     procs = []
-    bdir = os.path.join(HERE, "build" if out == LIB else "build_dev")
+    bdir = os.path.join(HERE, "build")
     os.makedirs(bdir, exist_ok=True)
     for src in SOURCES:
         obj = os.path.join(bdir, src.replace(".cu", ".o"))
         objs.append(obj)
-        cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas=-v")
         procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
@@ -62,8 +61,8 @@ def build(force: bool = False, verbose: bool = False, extra_flags=(), out: str =
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed")
-    subprocess.check_call([nvcc, "-arch=sm_100a", "-shared", "-o", out, *objs])
-    return out
+    subprocess.check_call([nvcc, "-arch=sm_100a", "-shared", "-o", LIB, *objs])
+    return LIB
 
 
 if __name__ == "__main__":

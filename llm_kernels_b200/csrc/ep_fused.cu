@@ -22,11 +22,14 @@ constexpr int kPlanThreads = 1024;
 
 // One block.  counts[s * E + e]: slots rank s routes to global expert e (owner e / El).
 //   dst_base[e]        byte address, in owner(e)'s receive buffer, of my first record for expert e
-//                      (0 when the owner's capacity would be exceeded: those records are dropped
-//                      and info[1] is set)
+//                      (0 when that block does not fit: its records are dropped and info[1] is set)
 //   local_seg[El + 1]  my group table: rows of local expert el are [local_seg[el], local_seg[el+1])
 //   blk_start[El*ep+1] first receive row of block (el, s);  blk_dst[El*ep] return address of that row
-//   info[0] rows received (clamped to the capacity), info[1] overflow flag
+//   info[0] rows received, info[1] overflow flag
+// Capacity rule, the same on both sides: the block (expert e, source s) is accepted iff it fits whole,
+// start + count <= cap_rows.  Block starts grow with (e, s), so the accepted blocks are a prefix of the
+// owner's buffer: the owner computes only rows below the first rejected block's start, the source writes no
+// record of a rejected block (and zero-fills the return rows of those slots, permute_quant_fp8_push).
 __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(
     const int64_t* __restrict__ counts, int rank, int ep, int E, int64_t cap_rows,
     const int64_t* __restrict__ recv_base, int64_t rec_bytes, const int64_t* __restrict__ back_base,
@@ -39,8 +42,9 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(
   int32_t* totpre = tot + E;       // [E + 1] exclusive prefix of tot
   const int El = E / ep;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+  __shared__ int valid_rows;       // start of the first rejected block of MY buffer (all rows if none)
   for (int i = tid; i < ep * E; i += blockDim.x) c[i] = static_cast<int32_t>(counts[i]);
-  if (tid == 0) { info[0] = 0; info[1] = 0; }
+  if (tid == 0) { info[0] = 0; info[1] = 0; valid_rows = 0x7fffffff; }
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x) {
     int t = 0;
@@ -73,22 +77,33 @@ __global__ void __launch_bounds__(kPlanThreads) ep_plan_kernel(
     dst_base[e] = fits ? recv_base[d] + row * rec_bytes : 0;
     if (!fits && c[rank * E + e] > 0) info[1] = 1;
   }
+  for (int el = tid; el < El; el += blockDim.x) {          // first rejected block of my own buffer
+    const int e = rank * El + el;
+    int64_t run = totpre[e] - totpre[rank * El];
+    for (int s = 0; s < ep; ++s) {
+      const int cnt = c[s * E + e];
+      if (cnt > 0 && run + cnt > cap_rows) { atomicMin(&valid_rows, static_cast<int>(min(run, cap_rows))); break; }
+      run += cnt;
+    }
+  }
+  __syncthreads();
+  const int64_t all_rows = totpre[rank * El + El] - totpre[rank * El];
+  const int64_t valid = min(static_cast<int64_t>(valid_rows), all_rows);
   for (int el = tid; el < El; el += blockDim.x) {
     const int e = rank * El + el;
     const int64_t ls = totpre[e] - totpre[rank * El];
-    local_seg[el] = min(ls, cap_rows);
+    local_seg[el] = min(ls, valid);
     int64_t run = ls;
     for (int s = 0; s < ep; ++s) {
-      blk_start[el * ep + s] = static_cast<int32_t>(min(run, cap_rows));
+      blk_start[el * ep + s] = static_cast<int32_t>(min(run, valid));
       blk_dst[el * ep + s] = back_base[s] + static_cast<int64_t>(pre[s * E + e]) * back_row_bytes;
       run += c[s * E + e];
     }
     if (el == El - 1) {
-      const int64_t total = min(run, cap_rows);
-      local_seg[El] = total;
-      blk_start[El * ep] = static_cast<int32_t>(total);
-      info[0] = static_cast<int32_t>(total);
-      if (run > cap_rows) info[1] = 1;
+      local_seg[El] = valid;
+      blk_start[El * ep] = static_cast<int32_t>(valid);
+      info[0] = static_cast<int32_t>(valid);
+      if (valid < all_rows) info[1] = 1;
     }
   }
 }
@@ -122,25 +137,32 @@ template <typename TI>
 __global__ void __launch_bounds__(256) permute_quant_fp8_push_kernel(
     const TI* __restrict__ x, const int32_t* __restrict__ src2dst, const int64_t* __restrict__ topk_ids,
     const int64_t* __restrict__ seg, const int64_t* __restrict__ dst_base, int num_experts, int topk,
-    int64_t H, int64_t rec_bytes) {
+    int64_t H, int64_t rec_bytes, uint8_t* __restrict__ back_local, int64_t back_row_bytes) {
   extern __shared__ __align__(128) uint8_t s_rec[];
   __shared__ int64_t s_addr[kMaxTopK];
-  __shared__ int s_n;
+  __shared__ int32_t s_drop[kMaxTopK];
+  __shared__ int s_n, s_nd;
   const int64_t t = blockIdx.x;
   if (threadIdx.x == 0) {
-    int n = 0;
+    int n = 0, nd = 0;
     for (int j = 0; j < topk; ++j) {
       const int64_t e = topk_ids[t * topk + j];
       const int32_t d = src2dst[t * topk + j];
       if (e < 0 || e >= num_experts || d < 0) continue;
       const int64_t base = dst_base[e];
-      if (base == 0) continue;                       // owner's buffer is full: dropped, flagged by ep_plan
+      if (base == 0) { s_drop[nd++] = d; continue; }   // the owner's buffer is full: dropped, flagged by ep_plan
       s_addr[n++] = base + (static_cast<int64_t>(d) - seg[e]) * rec_bytes;
     }
-    s_n = n;
+    s_n = n; s_nd = nd;
   }
   __syncthreads();
   const int n = s_n;
+  // a dropped slot gets no result back: its row of my return buffer is cleared, so the un-permute adds zeros
+  // instead of what an earlier step left there
+  if (back_local)
+    for (int j = 0; j < s_nd; ++j)
+      for (int64_t b = threadIdx.x * 16; b < back_row_bytes; b += blockDim.x * 16)
+        *reinterpret_cast<uint4*>(back_local + static_cast<int64_t>(s_drop[j]) * back_row_bytes + b) = make_uint4(0, 0, 0, 0);
   if (n == 0) return;
   const int64_t chunks = H / 8;
   const int64_t padded = (chunks + 31) & ~int64_t(31);
@@ -220,7 +242,8 @@ extern "C" int b200moe_ep_plan(const int64_t* counts_all, int rank, int ep_size,
 extern "C" int b200moe_permute_quant_fp8_push(const void* x, int x_dtype, const int32_t* src2dst,
                                               const int64_t* topk_ids, const int64_t* seg_indptr,
                                               const int64_t* dst_base, int num_experts, int64_t T, int topk,
-                                              int64_t H, int64_t rec_bytes, void* stream) {
+                                              int64_t H, int64_t rec_bytes, void* back_local,
+                                              int64_t back_row_bytes, void* stream) {
   if (T == 0) return B200MOE_OK;      // an empty batch has no buffers to check
   B200MOE_REQUIRE(x && src2dst && topk_ids && seg_indptr && dst_base, B200MOE_BAD_ARG, "permute_quant_fp8_push: null pointer");
   B200MOE_REQUIRE(T >= 0 && H > 0 && H % 128 == 0, B200MOE_BAD_SHAPE,
@@ -228,26 +251,29 @@ extern "C" int b200moe_permute_quant_fp8_push(const void* x, int x_dtype, const 
   B200MOE_REQUIRE(topk >= 1 && topk <= kMaxTopK, B200MOE_BAD_SHAPE, "permute_quant_fp8_push: topk=%d", topk);
   B200MOE_REQUIRE(rec_bytes >= H + (H / 128) * 4 && rec_bytes % 16 == 0 && aligned(x, 16), B200MOE_BAD_ARG,
                   "permute_quant_fp8_push: record of %lld bytes for hidden_size %lld", (long long)rec_bytes, (long long)H);
+  B200MOE_REQUIRE(back_local == nullptr || (aligned(back_local, 16) && back_row_bytes > 0 && back_row_bytes % 16 == 0),
+                  B200MOE_BAD_ALIGN, "permute_quant_fp8_push: return buffer rows must be 16-byte multiples");
   if (T == 0) return B200MOE_OK;
   cudaStream_t st = as_stream(stream);
   const int64_t chunks = H / 8;
   const int th = chunks >= 256 ? 256 : static_cast<int>((chunks + 31) / 32 * 32);
   const unsigned grid = static_cast<unsigned>(T);
   const size_t smem = static_cast<size_t>(rec_bytes);
+  uint8_t* bl = static_cast<uint8_t*>(back_local);
   B200MOE_REQUIRE(rec_bytes <= 40 * 1024, B200MOE_BAD_SHAPE, "permute_quant_fp8_push: record of %lld bytes (max 40960)",
                   (long long)rec_bytes);
   switch (x_dtype) {
     case B200MOE_BF16:
       permute_quant_fp8_push_kernel<__nv_bfloat16><<<grid, th, smem, st>>>(static_cast<const __nv_bfloat16*>(x), src2dst, topk_ids,
-                                                                        seg_indptr, dst_base, num_experts, topk, H, rec_bytes);
+                                                                        seg_indptr, dst_base, num_experts, topk, H, rec_bytes, bl, back_row_bytes);
       break;
     case B200MOE_F16:
       permute_quant_fp8_push_kernel<__half><<<grid, th, smem, st>>>(static_cast<const __half*>(x), src2dst, topk_ids,
-                                                                 seg_indptr, dst_base, num_experts, topk, H, rec_bytes);
+                                                                 seg_indptr, dst_base, num_experts, topk, H, rec_bytes, bl, back_row_bytes);
       break;
     case B200MOE_F32:
       permute_quant_fp8_push_kernel<float><<<grid, th, smem, st>>>(static_cast<const float*>(x), src2dst, topk_ids,
-                                                                seg_indptr, dst_base, num_experts, topk, H, rec_bytes);
+                                                                seg_indptr, dst_base, num_experts, topk, H, rec_bytes, bl, back_row_bytes);
       break;
     default:
       return fail(B200MOE_BAD_DTYPE, "permute_quant_fp8_push: x dtype %d", x_dtype);

@@ -91,6 +91,8 @@ struct GemmParams {
   // when it adds this GEMM's output to a tensor of the same dtype (shared experts added to the
   // routed output, moe/all2all_moe.py:182-183)
   int accumulate;
+  // fused gate/up epilogues (swiglu != 0): 0 = SiLU, 1 = tanh-GELU
+  int act;
 };
 
 struct Tile { int m0, m_end, expert, nt, ks; };
@@ -153,6 +155,15 @@ __device__ __forceinline__ void store_row64<__half>(__half* dst, const float* v)
 }
 
 __device__ __forceinline__ float bf16r(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+// Activation of the fused "act(gate) * up" epilogues, evaluated in f32 on the bf16-rounded gate value:
+// act 0 = SiLU (moe/group_gemm_kernel.py:158-162), act 1 = tanh-GELU with tanh(x) = 2 sigmoid(2x) - 1 (:176-224).
+__device__ __forceinline__ float gate_act(float g, int act) {
+  if (act == 0) return g * __fdividef(1.0f, 1.0f + __expf(-g));
+  const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+  const float th = 2.f * __fdividef(1.0f, 1.0f + __expf(-2.f * inner)) - 1.f;
+  return 0.5f * g * (1.f + th);
+}
 
 // Operand kinds.  All three share the pipeline; K is counted in bytes (128 per K block).
 //   kFp8  e4m3 x e4m3 -> f32, per-K-block promotion with f32 scales
@@ -556,7 +567,7 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         for (int j = 0; j < 64; ++j) {
           const float g = bf16r(acc[j]);
           const float u = bf16r(acc[64 + j]);
-          const float a = bf16r(g * __fdividef(1.0f, 1.0f + __expf(-g)));
+          const float a = bf16r(gate_act(g, p.act));
           acc[j] = a * u;
         }
         if (row_ok) {
@@ -571,7 +582,7 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
         for (int j = 0; j < 64; ++j) {
           const float g = bf16r(acc[j]);
           const float u = bf16r(acc[64 + j]);
-          const float a = bf16r(g * __fdividef(1.0f, 1.0f + __expf(-g)));
+          const float a = bf16r(gate_act(g, p.act));
           const float h = bf16r(a * u);
           acc[j] = h;
           amax = fmaxf(amax, fabsf(h));
@@ -690,7 +701,7 @@ extern "C" int b200moe_gemm_fp8_block(const void* a, const float* a_s, const voi
   if (M == 0) return B200MOE_OK;
   const int esz = c_dtype == B200MOE_F32 ? 4 : 2;
   GemmParams p{a_s, K / 128, b_s, c, N * esz, nullptr, 0, nullptr, nullptr, M,
-               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr, nullptr, 0};
+               static_cast<int>(N), static_cast<int>(K), 1, 1, c_dtype, 0, nullptr, 1, 0, 0, nullptr, nullptr, 0, 0};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   return launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream));
 }
@@ -740,7 +751,7 @@ extern "C" int b200moe_gemm_fp8_block_splitk(const void* a, const float* a_s, co
   if (M == 0) return B200MOE_OK;
   GemmParams p{a_s, K / 128, b_s, partials, N * 4, nullptr, 0, nullptr, nullptr, M,
                static_cast<int>(N), static_cast<int>(K), 1, 1, B200MOE_F32, 0, nullptr, ksplits, M * N * 4, 0,
-               nullptr, nullptr, 0};
+               nullptr, nullptr, 0, 0};
   const int64_t tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN) * ksplits;
   if (int rc = launch_gemm<kFp8>(a, K, b, p, tiles, as_stream(stream))) return rc;
   const int64_t n = M * N;
@@ -765,7 +776,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
                   "grouped_gemm_fp8: c_row_map / c_row_addr need epilogue 0");
   B200MOE_REQUIRE(c_row_map == nullptr || c_row_addr == nullptr, B200MOE_BAD_ARG,
                   "grouped_gemm_fp8: c_row_map and c_row_addr are exclusive");
-  B200MOE_REQUIRE(epilogue == 0 || epilogue == 1, B200MOE_BAD_ARG, "grouped_gemm_fp8: epilogue %d", epilogue);
+  B200MOE_REQUIRE(epilogue == 0 || epilogue == 1 || epilogue == 4, B200MOE_BAD_ARG, "grouped_gemm_fp8: epilogue %d", epilogue);
   B200MOE_REQUIRE(M_total >= 0 && M_total < (int64_t(1) << 31) && N > 0 && K > 0 && K % 128 == 0 && N % 128 == 0,
                   B200MOE_BAD_SHAPE, "grouped_gemm_fp8: M=%lld N=%lld K=%lld (N and K must be multiples of 128)",
                   (long long)M_total, (long long)N, (long long)K);
@@ -776,7 +787,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
                   a_row_stride_bytes >= K && c_row_stride_bytes % 16 == 0,
                   B200MOE_BAD_ALIGN, "grouped_gemm_fp8: pointers and row strides must be 16-byte aligned");
   B200MOE_REQUIRE(a_s_row_stride >= K / 128, B200MOE_BAD_ARG, "grouped_gemm_fp8: a_s row stride too small");
-  if (epilogue == 1) {
+  if (epilogue != 0) {
     B200MOE_REQUIRE(N % 256 == 0, B200MOE_BAD_SHAPE, "grouped_gemm_fp8: the SwiGLU epilogue needs N %% 256 == 0, got %lld", (long long)N);
     B200MOE_REQUIRE(c_dtype == B200MOE_FP8_E4M3 && c_s && c_row_stride_bytes >= N / 2 && c_s_row_stride >= N / 256,
                     B200MOE_BAD_ARG, "grouped_gemm_fp8: the SwiGLU epilogue writes e4m3 rows and f32 scales");
@@ -788,7 +799,8 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, c_s, c_s_row_stride, seg_indptr,
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
-               num_weights, c_dtype, epilogue, status_word, 1, 0, 0, c_row_map, c_row_addr, 0};
+               num_weights, c_dtype, epilogue == 4 ? 1 : epilogue, status_word, 1, 0, 0, c_row_map, c_row_addr, 0,
+               epilogue == 4 ? 1 : 0};
   return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -823,7 +835,7 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
                   B200MOE_BAD_ARG, "grouped_gemm_i8: c row stride");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr, nullptr, 0};
+               static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr, nullptr, 0, 0};
   return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
 
@@ -834,11 +846,11 @@ static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_byte
                               int epilogue, int32_t* status_word, void* stream) {
   if (int rc = check_grouped_common("grouped_gemm_bf16", a, b, c, seg_indptr, a_row_stride_bytes, 2 * K, M_total, N,
                                     num_groups, num_weights)) return rc;
-  B200MOE_REQUIRE(epilogue == 0 || epilogue == 3 || (epilogue == 2 && !f16), B200MOE_BAD_ARG,
-                  "grouped_gemm_bf16: epilogue %d (0 plain, 2 SwiGLU with bf16 operands, 3 plain added to c)", epilogue);
+  B200MOE_REQUIRE(epilogue == 0 || epilogue == 3 || ((epilogue == 2 || epilogue == 5) && !f16), B200MOE_BAD_ARG,
+                  "grouped_gemm_bf16: epilogue %d (0 plain, 2 SiLU*up / 5 GELU*up with bf16 operands, 3 plain added to c)", epilogue);
   B200MOE_REQUIRE(epilogue != 3 || c_dtype == B200MOE_BF16 || c_dtype == B200MOE_F16, B200MOE_BAD_DTYPE,
                   "grouped_gemm_bf16: epilogue 3 adds into a 16-bit c");
-  if (epilogue == 2) {
+  if (epilogue == 2 || epilogue == 5) {
     B200MOE_REQUIRE(N % 256 == 0 && c_dtype == B200MOE_BF16 && c_row_stride_bytes >= N, B200MOE_BAD_ARG,
                     "grouped_gemm_bf16: the SwiGLU epilogue needs N %% 256 == 0 and a bf16 [M, N/2] output");
   } else {
@@ -849,8 +861,9 @@ static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_byte
   B200MOE_REQUIRE(c_row_stride_bytes % 16 == 0, B200MOE_BAD_ALIGN, "grouped_gemm_bf16: c row stride alignment");
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
-               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype, epilogue == 3 ? 0 : epilogue,
-               status_word, 1, 0, 0, nullptr, nullptr, epilogue == 3 ? 1 : 0};
+               static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype,
+               epilogue == 3 ? 0 : (epilogue == 5 ? 2 : epilogue), status_word, 1, 0, 0, nullptr, nullptr,
+               epilogue == 3 ? 1 : 0, epilogue == 5 ? 1 : 0};
   return f16 ? launch_gemm<kF16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream))
              : launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
 }
@@ -892,7 +905,7 @@ extern "C" int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_b
   if (T == 0) return B200MOE_OK;
   GemmParams p{nullptr, 0, nullptr, partials, static_cast<int64_t>(E) * 4, nullptr, 0, nullptr, nullptr, T, E,
                static_cast<int>(3 * H * 2), 1, 1, B200MOE_F32, 0, nullptr, ksplits, T * static_cast<int64_t>(E) * 4,
-               static_cast<int>(H * 2), nullptr, nullptr, 0};
+               static_cast<int>(H * 2), nullptr, nullptr, 0, 0};
   const int64_t tiles = ((T + BM - 1) / BM) * ((E + BN - 1) / BN) * ksplits;
   return launch_gemm<kBf16>(x_bf16, H * 2, w3_bf16, p, tiles, as_stream(stream));
 }

@@ -8,6 +8,7 @@
 //   [N, K/128]:  w[n,k] = bf16( (q - zero) * scale )
 // Both are HBM-bound one-pass kernels over a stack of W matrices.
 #include "common.cuh"
+#include "marlin_perm.cuh"
 
 namespace b200moe {
 
@@ -65,11 +66,9 @@ __global__ void __launch_bounds__(256) w4a16_expand_kernel(const uint32_t* __res
 // [K/16, N*16/8].  A packed row holds one 16-row k-tile, tiles of 16 x 16 flattened as
 // n_tile*256 + k_in*16 + n_in, permuted in blocks of 1024 by `perm` (packed position i holds
 // element perm[i]) and packed 8 nibbles per word.  Scales f16 [K/g, N] are permuted in blocks of
-// 64 (grouped) or 32 (one group) columns.  One thread expands one word into
+// 64 (grouped) or 32 (one group) columns; both permutations are closed forms (marlin_perm.cuh), so calls
+// share no state.  One thread expands one word into
 // out[n, k] = (q - 8) * s[k/g, n]  (f16, nn.Linear layout [N, K]).
-__constant__ int16_t c_marlin_perm[1024];
-__constant__ int8_t c_marlin_sinv[64];     // inverse scale permutation (first L entries used)
-
 __global__ void __launch_bounds__(256) marlin_expand_kernel(const uint32_t* __restrict__ packed,
                                                             const __half* __restrict__ s,
                                                             __half* __restrict__ out, int64_t K,
@@ -83,11 +82,11 @@ __global__ void __launch_bounds__(256) marlin_expand_kernel(const uint32_t* __re
 #pragma unroll
     for (int f = 0; f < 8; ++f) {
       const int64_t pcol = j * 8 + f;
-      const int64_t c = (pcol / 1024) * 1024 + c_marlin_perm[pcol % 1024];
+      const int64_t c = (pcol / 1024) * 1024 + marlin_perm(static_cast<int>(pcol % 1024));
       const int64_t n = (c / 256) * 16 + (c % 16);
       const int64_t k = r * 16 + (c % 256) / 16;
       const int64_t g = groupsize > 0 ? k / groupsize : 0;
-      const float sc = __half2float(s[g * N + (n / L) * L + c_marlin_sinv[n % L]]);
+      const float sc = __half2float(s[g * N + (n / L) * L + (L == 64 ? marlin_scale_inv64(static_cast<int>(n % L)) : marlin_scale_inv32(static_cast<int>(n % L)))]);
       const int q = static_cast<int>((word >> (4 * f)) & 0xF);
       out[n * K + k] = __float2half_rn(static_cast<float>(q - 8) * sc);
     }
@@ -99,20 +98,15 @@ __global__ void __launch_bounds__(256) marlin_expand_kernel(const uint32_t* __re
 using namespace b200moe;
 
 extern "C" int b200moe_marlin_expand_f16(const void* packed, const void* scales_f16, void* out_f16,
-                                         int64_t K, int64_t N, int64_t groupsize, const int16_t* perm1024,
-                                         const int8_t* scale_perm_inverse, int scale_perm_len, void* stream) {
-  B200MOE_REQUIRE(packed && scales_f16 && out_f16 && perm1024 && scale_perm_inverse, B200MOE_BAD_ARG,
-                  "marlin_expand_f16: null pointer");
+                                         int64_t K, int64_t N, int64_t groupsize, void* stream) {
+  B200MOE_REQUIRE(packed && scales_f16 && out_f16, B200MOE_BAD_ARG, "marlin_expand_f16: null pointer");
   B200MOE_REQUIRE(K > 0 && N > 0 && K % 16 == 0 && N % 64 == 0 && (N * 16) % 1024 == 0, B200MOE_BAD_SHAPE,
                   "marlin_expand_f16: Matrix dimensions not compatible with Marlin kernel requirements (K=%lld N=%lld)",
                   (long long)K, (long long)N);
   B200MOE_REQUIRE(groupsize == -1 || (groupsize > 0 && K % groupsize == 0), B200MOE_BAD_SHAPE,
                   "marlin_expand_f16: K dimension not divisible by groupsize: K=%lld, groupsize=%lld", (long long)K, (long long)groupsize);
-  B200MOE_REQUIRE(scale_perm_len == 64 || scale_perm_len == 32, B200MOE_BAD_ARG, "marlin_expand_f16: scale permutation length %d", scale_perm_len);
-  // the tables are host arrays; they are tiny and re-uploaded per call on the given stream
   cudaStream_t st = as_stream(stream);
-  cudaMemcpyToSymbolAsync(c_marlin_perm, perm1024, 1024 * sizeof(int16_t), 0, cudaMemcpyHostToDevice, st);
-  cudaMemcpyToSymbolAsync(c_marlin_sinv, scale_perm_inverse, scale_perm_len, 0, cudaMemcpyHostToDevice, st);
+  const int scale_perm_len = groupsize == -1 ? 32 : 64;
   const int64_t total = (K / 16) * N * 2;
   const unsigned grid = static_cast<unsigned>(std::min<int64_t>((total + 255) / 256, 148 * 32));
   marlin_expand_kernel<<<grid, 256, 0, st>>>(static_cast<const uint32_t*>(packed), static_cast<const __half*>(scales_f16),

@@ -5,25 +5,12 @@ The reference streams the packed weights through mma.sync fragments.  Here a CUD
 nibbles to f16 in nn.Linear layout, `(q - 8) * scale` rounded to f16 exactly as the reference's
 dequantization (marlin_w4a16_gemm.cu:44-64), and the product runs on the tcgen05 f16 path with f32
 accumulation.  The expansion is cached per packed tensor, keyed on storage and version."""
-import ctypes
 from typing import Dict, Tuple
 
 import torch
 
 from ... import _native as N
-from .utils import _perm, scale_perm_for
 
-_PERM16 = (ctypes.c_int16 * 1024)(*[int(v) for v in _perm])
-
-
-def _inverse(p) -> "ctypes.Array":
-    inv = [0] * len(p)
-    for i, v in enumerate(p):
-        inv[v] = i
-    return (ctypes.c_int8 * len(p))(*inv)
-
-
-_SINV = {64: _inverse(scale_perm_for(128)), 32: _inverse(scale_perm_for(-1))}
 _cache: Dict[Tuple[int, int, int, int], torch.Tensor] = {}
 
 
@@ -33,12 +20,9 @@ def expand(B: torch.Tensor, s: torch.Tensor, K: int, Nn: int, groupsize: int) ->
     N.require_cuda(B, s)
     assert B.dtype == torch.int32 and s.dtype == torch.half and B.is_contiguous() and s.is_contiguous()
     assert tuple(B.shape) == (K // 16, Nn * 2), f"packed shape {tuple(B.shape)} for K={K} N={Nn}"
-    L = 32 if groupsize == -1 else 64
     assert s.numel() == (1 if groupsize == -1 else K // groupsize) * Nn
     out = torch.empty(Nn, K, dtype=torch.half, device=B.device)
-    N.check(N.lib().b200moe_marlin_expand_f16(N.ptr(B), N.ptr(s), N.ptr(out), K, Nn, groupsize,
-                                              ctypes.cast(_PERM16, ctypes.c_void_p),
-                                              ctypes.cast(_SINV[L], ctypes.c_void_p), L, N.stream()))
+    N.check(N.lib().b200moe_marlin_expand_f16(N.ptr(B), N.ptr(s), N.ptr(out), K, Nn, groupsize, N.stream()))
     return out
 
 

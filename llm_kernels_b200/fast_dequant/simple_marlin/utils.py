@@ -1,8 +1,8 @@
 """Offline int4 quantization and Marlin-order packing (reference: fast_dequant/simple_marlin/utils.py).
 
 `QuantUtils.fake_quantize` and `QuantUtils.pack` keep the reference's signatures and produce the same
-tensors bit for bit; both run on the device the weight lives on (the reference packs through numpy on
-the host)."""
+tensors bit for bit.  `pack` of CUDA tensors is a CUDA kernel; host tensors are packed on the host with
+torch ops, as the reference packs them through numpy."""
 from typing import List, Tuple
 
 import torch
@@ -41,6 +41,15 @@ class QuantUtils:
         assert weight.dtype == torch.int, f"weight dtype {weight.dtype} != torch.int"
         assert weight.shape[0] % groupsize == 0, "Weight shape must be divisible by groupsize"
         k, n = weight.shape
+        if weight.is_cuda:
+            from ... import _native as N
+            assert scale.dtype == torch.half and scale.is_cuda and k % 16 == 0 and n % 64 == 0
+            weight, scale = weight.contiguous(), scale.contiguous()
+            packed = torch.empty(k // 16, n * 2, dtype=torch.int32, device=weight.device)
+            scale_out = torch.empty(scale.numel() // n, n, dtype=torch.half, device=weight.device)
+            N.check(N.lib().b200moe_marlin_pack(N.ptr(weight), N.ptr(packed), N.ptr(scale), N.ptr(scale_out), k, n,
+                                                groupsize, N.stream()))
+            return packed, scale_out
         sp = scale_perm_for(groupsize)
         scale = scale.reshape(-1, len(sp))[:, sp].reshape(-1, n).contiguous()
         tiles = weight.reshape(k // 16, 16, n // 16, 16).permute(0, 2, 1, 3).reshape(k // 16, n * 16)

@@ -49,8 +49,9 @@ class DeepseekV3MLP(nn.Module):
         self.config = config
         self.hidden_size = config.hidden_size if hidden_size is None else hidden_size
         self.intermediate_size = config.intermediate_size if intermediate_size is None else intermediate_size
-        if getattr(config, "hidden_act", "silu") != "silu":
-            raise NotImplementedError("the fused epilogue implements silu")
+        self.hidden_act = getattr(config, "hidden_act", "silu")
+        if self.hidden_act not in ("silu", "gelu"):
+            raise NotImplementedError(f"hidden_act {self.hidden_act!r}: the fused epilogues implement silu and gelu")
         self.gate_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
         self.up_proj = nn.Linear(self.hidden_size, self.intermediate_size, bias=False)
         self.down_proj = nn.Linear(self.intermediate_size, self.hidden_size, bias=False)
@@ -77,7 +78,7 @@ class DeepseekV3MLP(nn.Module):
         M = x2.shape[0]
         seg = torch.tensor([0, M], dtype=torch.int64, device=x.device)
         h = torch.empty(M, I, dtype=torch.bfloat16, device=x.device)
-        G.grouped_gemm_bf16(x2, self._fused_gate_up(), seg, None, h, epilogue=2)
+        G.grouped_gemm_bf16(x2, self._fused_gate_up(), seg, None, h, epilogue=2 if self.hidden_act == "silu" else 5)
         y = torch.empty(M, H, dtype=torch.bfloat16, device=x.device)
         G.grouped_gemm_bf16(h, self.down_proj.weight.detach().unsqueeze(0), seg, None, y, epilogue=0)
         return y.view(*x.shape[:-1], H)
@@ -190,8 +191,11 @@ class DeepseekV3MoE(nn.Module):
         self.method = getattr(config, "quantize_method", "fp8_block")
         if self.method not in self.METHODS:
             raise NotImplementedError(f"quantize_method {self.method!r}")
-        if getattr(config, "hidden_act", "silu") != "silu":
-            raise NotImplementedError("the fused GEMM-1 epilogue implements silu")
+        # activation of the expert FFNs (reference moe/sglang_moe_all_gather_all_reduce.py:374-397): SiLU or tanh-GELU
+        self.hidden_act = getattr(config, "hidden_act", "silu")
+        if self.hidden_act not in ("silu", "gelu"):
+            raise NotImplementedError(f"hidden_act {self.hidden_act!r}: the fused GEMM-1 epilogues implement silu and gelu")
+        self._gelu = self.hidden_act == "gelu"
         if hasattr(config, "ep_size") and config.ep_size > 1:
             assert config.ep_size == dist.get_world_size()
             self.ep_size = config.ep_size
@@ -327,7 +331,8 @@ class DeepseekV3MoE(nn.Module):
         h = self._buf("shared_h", (T, Is), torch.bfloat16)
         side.wait_stream(main)
         with torch.cuda.stream(side):
-            G.grouped_gemm_bf16(x, self.shared_w13, seg, None, h, epilogue=2, status_word=self._status)
+            G.grouped_gemm_bf16(x, self.shared_w13, seg, None, h, epilogue=5 if self._gelu else 2,
+                                status_word=self._status)
             ev = torch.cuda.Event()
             ev.record(side)
         return h, seg, ev
@@ -573,11 +578,15 @@ class DeepseekV3MoE(nn.Module):
                                              smax, H, E)
         fx = self._fx
         assert S <= fx.slots, f"{S} routed slots, peer buffers were sized for {fx.slots} at the first call"
+        # the previous forward's overflow flag has long reached the host (copied there right after its plan
+        # kernel): a batch whose rows did not fit a peer buffer raises here instead of passing for a result
+        fx.raise_if_overflowed()
         fx.gather_counts(seg_indptr)
         G.ep_plan(fx.counts_all, self.ep_rank, ep, fx.cap_rows, fx.recv_base, rec, fx.back_base, H * 2,
                   out=(fx.dst_base, fx.local_seg, fx.back_addr, fx.info))
+        fx.publish_info()
         self._mark("exchange_plan")
-        G.permute_quant_fp8_push(x, src2dst, ids, seg_indptr, fx.dst_base, rec)
+        G.permute_quant_fp8_push(x, src2dst, ids, seg_indptr, fx.dst_base, rec, back_local=fx.back)
         fx.barrier()                                         # every rank's records have landed
         self._mark("permute_quant")
         self._last_recv_rows = fx.info[0]
@@ -661,7 +670,7 @@ class DeepseekV3MoE(nn.Module):
         h_q = self._buf("h_q", (rows, I), torch.uint8)
         h_s = self._buf("h_s", (rows, I // 128), torch.float32)
         G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx,
-                           h_q, h_s, epilogue=1, status_word=self._status)
+                           h_q, h_s, epilogue=4 if self._gelu else 1, status_word=self._status)
         self._mark("gemm1_swiglu")
         G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx,
                            down, None, epilogue=0, status_word=self._status, c_row_map=ctx.get("c_row_map"),
@@ -676,7 +685,7 @@ class DeepseekV3MoE(nn.Module):
             ctx["w2"] = w4a16_kernel.expand_bf16(self.w2_qweight, self.w2_scale, self.w2_zero)
             self._mark("expand_weights")
         h = self._buf("h_bf16", (rows, I), torch.bfloat16)
-        G.grouped_gemm_bf16(a, ctx["w13"], seg, widx, h, epilogue=2, status_word=self._status)
+        G.grouped_gemm_bf16(a, ctx["w13"], seg, widx, h, epilogue=5 if self._gelu else 2, status_word=self._status)
         self._mark("gemm1_swiglu")
         G.grouped_gemm_bf16(h, ctx["w2"], seg, widx, down, epilogue=0, status_word=self._status)
         self._mark("gemm2")
@@ -693,7 +702,8 @@ class DeepseekV3MoE(nn.Module):
         self._mark("gemm1")
         r0, r1 = rng                                   # the rows this call's groups cover
         h = self._buf("h_bf16", (rows, I), torch.bfloat16)
-        G.silu_and_mul_triton_kernel[(r1 - r0,)](gu[r0:r1], h[r0:r1], 2 * I, None, None, 0, 0, BLOCK_SIZE=512)
+        act_mul = G.gelu_and_mul_triton_kernel if self._gelu else G.silu_and_mul_triton_kernel
+        act_mul[(r1 - r0,)](gu[r0:r1], h[r0:r1], 2 * I, None, None, 0, 0, BLOCK_SIZE=512)
         h_q = self._buf("h_i8", (rows, I), torch.int8)
         h_s = self._buf("h_i8_s", (rows, I // 128), torch.float32)
         q, sc = w4a8_kernel.act_quant(h[r0:r1])
@@ -719,8 +729,8 @@ class DeepseekV3MoE(nn.Module):
         t1 = t2 = 0.0
         for _ in range(iters):
             ev[0].record()
-            G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx, h_q, h_s, epilogue=1,
-                               status_word=self._status)
+            G.grouped_gemm_fp8(a_q, a_s, self.w13_weight, self.w13_weight_scale, seg, widx, h_q, h_s,
+                               epilogue=4 if self._gelu else 1, status_word=self._status)
             ev[1].record()
             G.grouped_gemm_fp8(h_q, h_s, self.w2_weight, self.w2_weight_scale, seg, widx, down, None, epilogue=0,
                                status_word=self._status)
@@ -731,9 +741,14 @@ class DeepseekV3MoE(nn.Module):
         return t1 / iters, t2 / iters, rows
 
     def check_status(self):
-        """Raises if a kernel of an earlier forward reported a device-side timeout (synchronises)."""
-        if self._fx is not None and int(self._fx.info[1].item()):
-            raise N.B200MoeError(1, "a rank received more rows than its peer buffer holds; raise config.ep_recv_capacity")
+        """Raises if a kernel of an earlier forward reported a device-side timeout, or if rows of an earlier
+        forward did not fit a peer buffer of the fused exchange (synchronises).  With ep_exchange="fused" a
+        forward whose rows overflow `config.ep_recv_capacity` still completes -- the surplus rows contribute
+        zeros -- and the NEXT forward raises; call this after the last forward of a sequence so that its
+        overflow cannot go unnoticed either."""
+        if self._fx is not None:
+            torch.cuda.current_stream().synchronize()
+            self._fx.raise_if_overflowed()
         s = int(self._status.item())
         if s:
             self._status.zero_()

@@ -301,7 +301,26 @@ class FusedExchange:
         self.local_seg = torch.zeros(El + 1, dtype=torch.int64, device=device)
         self.back_addr = torch.zeros(cap_rows, dtype=torch.int64, device=device)
         self.info = torch.zeros(2, dtype=torch.int32, device=device)
+        self._info_host = torch.zeros(2, dtype=torch.int32).pin_memory()
+        self._info_event = None
         self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+
+    def publish_info(self):
+        """Queues a copy of the plan's {rows received, overflow flag} to pinned host memory behind the plan
+        kernel; raise_if_overflowed() reads it once the copy has completed."""
+        self._info_host.copy_(self.info, non_blocking=True)
+        self._info_event = torch.cuda.Event()
+        self._info_event.record()
+
+    def raise_if_overflowed(self):
+        if self._info_event is None:
+            return
+        self._info_event.synchronize()
+        self._info_event = None
+        if int(self._info_host[1]):
+            from .. import _native as N
+            raise N.B200MoeError(1, "expert-parallel exchange: a rank was sent more rows than its receive buffer "
+                                    "holds (those rows contributed zeros); raise config.ep_recv_capacity")
 
     def gather_counts(self, seg_indptr: torch.Tensor):
         counts = (seg_indptr[1:] - seg_indptr[:-1]).contiguous()

@@ -155,8 +155,8 @@ def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, ep
     """tcgen05 grouped blockwise GEMM on already-quantized activations.
     a [M,K] e4m3/uint8 (row-strided view allowed), a_s [M,K/128] f32 (row-strided view allowed),
     b [W,N,K] e4m3, b_s [W,N/128,K/128] f32, seg_indptr int64 [G+1], weight_indices int64 [G] or
-    None.  epilogue 0: c [M,N] bf16/f16/f32; epilogue 1 (SwiGLU + requant): c [M,N/2] e4m3,
-    c_s [M,N/256] f32.  c_row_map int32 [M] / c_row_addr int64 [M] (epilogue 0): row r is stored
+    None.  epilogue 0: c [M,N] bf16/f16/f32; epilogue 1 (SiLU(gate)*up + requant) / 4 (GELU(gate)*up +
+    requant): c [M,N/2] e4m3, c_s [M,N/256] f32.  c_row_map int32 [M] / c_row_addr int64 [M] (epilogue 0): row r is stored
     at row c_row_map[r] of c / at byte address c_row_addr[r] (possibly on another GPU)."""
     N.require_cuda(a, a_s, b, b_s, c)
     assert b.is_contiguous() and b_s.is_contiguous() and a.stride(1) == 1 and a_s.stride(1) == 1
@@ -165,7 +165,7 @@ def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, ep
     W, Nn, Kb = b.shape
     assert Kb == K
     G = seg_indptr.numel() - 1
-    c_dtype = N.FP8_E4M3 if epilogue == 1 else N.dtype_code(c.dtype)
+    c_dtype = N.FP8_E4M3 if epilogue in (1, 4) else N.dtype_code(c.dtype)
     N.check(N.lib().b200moe_grouped_gemm_fp8(
         N.ptr(a), a.stride(0) * a.element_size(), N.ptr(a_s), a_s.stride(0), N.ptr(b), N.ptr(b_s),
         N.ptr(c), c_dtype, c.stride(0) * c.element_size(),
@@ -197,15 +197,18 @@ def ep_plan(counts_all, rank, ep_size, cap_rows, recv_base, rec_bytes, back_base
     return out
 
 
-def permute_quant_fp8_push(x, src2dst, topk_ids, seg_indptr, dst_base, rec_bytes):
+def permute_quant_fp8_push(x, src2dst, topk_ids, seg_indptr, dst_base, rec_bytes, back_local=None):
     """permute_quant_fp8 storing every record at its owner: record of expert e at sorted position d
-    -> dst_base[e] + (d - seg_indptr[e]) * rec_bytes (payload, then f32 scales at byte H)."""
+    -> dst_base[e] + (d - seg_indptr[e]) * rec_bytes (payload, then f32 scales at byte H).  back_local
+    [slots, H] (this rank's return buffer): rows of dropped slots (dst_base[e] == 0) are cleared."""
     N.require_cuda(x, src2dst, topk_ids, seg_indptr, dst_base)
     T, H = x.shape
     assert x.is_contiguous() and topk_ids.dtype == torch.int64 and dst_base.dtype == torch.int64
     N.check(N.lib().b200moe_permute_quant_fp8_push(N.ptr(x), N.dtype_code(x.dtype), N.ptr(src2dst), N.ptr(topk_ids),
                                                    N.ptr(seg_indptr), N.ptr(dst_base), dst_base.numel(), T,
-                                                   topk_ids.shape[1], H, rec_bytes, N.stream()))
+                                                   topk_ids.shape[1], H, rec_bytes, N.ptr(back_local),
+                                                   0 if back_local is None else back_local.stride(0) * back_local.element_size(),
+                                                   N.stream()))
 
 
 def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=None):
@@ -226,8 +229,8 @@ def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=N
 
 def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, status_word=None):
     """tcgen05 grouped bf16 or f16 GEMM (reference: the scale-free branch of grouped_gemm_triton,
-    :410-412).  epilogue 0: c [M,N]; epilogue 2 (bf16 operands only): SwiGLU fused, c bf16 [M,N/2];
-    epilogue 3: c = round(c + round(a @ b^T)) for a 16-bit c."""
+    :410-412).  epilogue 0: c [M,N]; epilogue 2 / 5 (bf16 operands only): SiLU(gate)*up / GELU(gate)*up fused,
+    c bf16 [M,N/2]; epilogue 3: c = round(c + round(a @ b^T)) for a 16-bit c."""
     N.require_cuda(a, b, c)
     assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16)
     assert b.is_contiguous() and a.stride(1) == 1

@@ -10,7 +10,6 @@ from typing import Tuple
 import torch
 
 from .. import _native as N
-from . import bitpack
 
 
 def weight_quant(w: torch.Tensor, groupsize: int = 128) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
@@ -18,13 +17,13 @@ def weight_quant(w: torch.Tensor, groupsize: int = 128) -> Tuple[torch.Tensor, t
     scale = (max-min)/15, zero = round(-min/scale), q = clamp(round(w/scale) + zero, 0, 15)."""
     N.require_cuda(w)
     assert w.dim() == 2 and groupsize == 128 and w.shape[1] % 128 == 0
+    w = w.contiguous()
     Nn, K = w.shape
-    g = w.float().reshape(Nn, K // 128, 128)
-    mx, mn = g.amax(-1), g.amin(-1)
-    scale = ((mx - mn) / torch.full_like(mx, 15.0)).clamp_min(1e-8).to(torch.bfloat16)
-    zero = torch.round(-mn / scale.float()).clamp(0, 15).to(torch.bfloat16)
-    q = torch.clamp(torch.round(g / scale.float().unsqueeze(-1)) + zero.float().unsqueeze(-1), 0, 15)
-    packed, _ = bitpack.pack_weights_over_cols(q.reshape(Nn, K).to(torch.uint8), 4, 32, transpose=False)
+    packed = torch.empty(Nn, K // 8, dtype=torch.int32, device=w.device)
+    scale = torch.empty(Nn, K // 128, dtype=torch.bfloat16, device=w.device)
+    zero = torch.empty(Nn, K // 128, dtype=torch.bfloat16, device=w.device)
+    N.check(N.lib().b200moe_weight_quant_w4a16(N.ptr(w), N.dtype_code(w.dtype), N.ptr(packed), N.ptr(scale),
+                                               N.ptr(zero), Nn, K, N.stream()))
     return packed, scale, zero
 
 

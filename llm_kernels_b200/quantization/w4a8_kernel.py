@@ -3,23 +3,17 @@ quantization/w4a8_kernel.py (weight_quant :265-309, weight_dequant :104-142, act
 w4a8_gemm :406-448).
 
 The GEMM expands the packed int4 weights to int8 with a CUDA kernel and runs the tcgen05 int8
-GEMM with per-K-block f32 promotion.  weight_quant is offline preparation: its arithmetic runs as
-torch ops on the device, the packing through the bitpack kernel.
+GEMM with per-K-block f32 promotion.  weight_quant is one CUDA kernel (both levels and the packing).
 """
 from typing import Tuple
 
 import torch
 
 from .. import _native as N
-from . import bitpack, int8_kernel
+from . import int8_kernel
 
 PACKING_BITS = 32
 W_BITS = 4
-
-
-def _true_div(t: torch.Tensor, c: float) -> torch.Tensor:
-    # tensor / tensor is an IEEE division on CUDA; tensor / python-scalar is a reciprocal multiply
-    return t / torch.full_like(t, c)
 
 
 def weight_quant(x: torch.Tensor, block_size: int = 128, group_size_int4: int = 128,
@@ -33,18 +27,14 @@ def weight_quant(x: torch.Tensor, block_size: int = 128, group_size_int4: int = 
     assert pack_direction == "row", "Only row packing is supported"
     M, Nn = x.shape
     assert M % 128 == 0, 'row count must be divisible by 128'
-    blk = x.float().reshape(M // 128, 128, Nn // 128, 128).permute(0, 2, 1, 3)
-    s = _true_div(blk.abs().amax(dim=(-1, -2)), 119.0)
-    y8 = torch.clamp(torch.floor(blk / s[..., None, None] + 0.5), -119.0, 119.0)
-    y8 = y8.permute(0, 2, 1, 3).reshape(M, Nn)
-    g = y8.reshape(M, Nn // 128, 128)
-    mx, mn = g.amax(-1), g.amin(-1)
-    s4 = torch.floor(_true_div(mx - mn, 15.0) + 0.5)
-    z4 = torch.floor(-mn / s4 + 0.5)
-    q = torch.clamp(torch.floor(g / s4.unsqueeze(-1) + 0.5) + z4.unsqueeze(-1), 0, 15).reshape(M, Nn).to(torch.uint8)
-    assert M % (PACKING_BITS // W_BITS) == 0
-    packed, _ = bitpack.pack_weights_over_rows(q, W_BITS, PACKING_BITS, transpose=False)
-    return packed, s.to(torch.float16), s4.to(torch.int8), z4.to(torch.int8)
+    dev = x.device
+    packed = torch.empty(M // (PACKING_BITS // W_BITS), Nn, dtype=torch.int32, device=dev)
+    s = torch.empty(M // 128, Nn // 128, dtype=torch.float16, device=dev)
+    s4 = torch.empty(M, Nn // 128, dtype=torch.int8, device=dev)
+    z4 = torch.empty(M, Nn // 128, dtype=torch.int8, device=dev)
+    N.check(N.lib().b200moe_weight_quant_w4a8(N.ptr(x), N.dtype_code(x.dtype), N.ptr(packed), N.ptr(s), N.ptr(s4),
+                                              N.ptr(z4), M, Nn, N.stream()))
+    return packed, s, s4, z4
 
 
 def expand_int8(packed: torch.Tensor, s4: torch.Tensor, z4: torch.Tensor) -> torch.Tensor:

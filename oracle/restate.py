@@ -268,6 +268,27 @@ def act_quant_int8(x: torch.Tensor, block_size: int = 128, rounding: str = "half
             s.to(torch.float16).reshape(*x.shape[:-1], x.shape[-1] // block_size))
 
 
+def weight_quant_int8(x: torch.Tensor, block_size: int = 128):
+    """quantization/int8_kernel.py:59-113: per 128x128 block (edge blocks masked, :76-79)
+    s = amax/127 in fp32, y = libdevice.round(x / s) (half away from zero) as int8, s stored as
+    fp16 [ceil(M/128), ceil(N/128)].  The Triton kernel cannot run in the CPU interpreter
+    (libdevice), so this function is pinned by its formula only."""
+    M, N = x.shape
+    blk, _, _ = _blocks(x.float(), block_size)
+    s = _div_const(blk.abs().amax(dim=(-1, -2)), 127.0)
+    q = blk / s[..., None, None]
+    q = torch.sign(q) * torch.floor(q.abs() + 0.5)
+    q = q.permute(0, 2, 1, 3).reshape(blk.shape[0] * block_size, -1)[:M, :N]
+    return torch.nan_to_num(q, nan=0.0).to(torch.int8).contiguous(), s.to(torch.float16)
+
+
+def weight_dequant_int8(x: torch.Tensor, s: torch.Tensor, block_size: int = 128, dtype=torch.float32):
+    """quantization/int8_kernel.py:116-170: y = float(x) * s[i/128, j/128], cast to the default dtype."""
+    M, N = x.shape
+    se = s.float().repeat_interleave(block_size, 0)[:M].repeat_interleave(block_size, 1)[:, :N]
+    return (x.float() * se).to(dtype)
+
+
 # --------------------------------------------------------------------------
 # Reorder / activation / combine kernels  (moe/group_gemm_kernel.py)
 # --------------------------------------------------------------------------
@@ -369,7 +390,7 @@ def moe_infer_dense(x, topk_ids, topk_weight, gate_ws, up_ws, down_ws):
 
 
 def moe_layer_fp8(x, topk_ids, topk_weight, w13, w13_s, w2, w2_s, *,
-                  ep_size: int = 1, out_dtype=torch.bfloat16):
+                  ep_size: int = 1, out_dtype=torch.bfloat16, hidden_act: str = "silu"):
     """The quantized expert-parallel layer the B200 path implements, restated
     from the reference's pieces:
 
@@ -382,8 +403,9 @@ def moe_layer_fp8(x, topk_ids, topk_weight, w13, w13_s, w2, w2_s, *,
                     ranks so per-rank segment bookkeeping is exercised
       GEMM-1        grouped blockwise GEMM with w13 = [gate ; up]
                     (moe/moe_numerical_equivalence_validation.py:87-88)
-      activation    moe/group_gemm_kernel.py:120-168 (intermediate rounded to
-                    out_dtype as the reference's gateup_output is)
+      activation    moe/group_gemm_kernel.py:120-168 (silu) or :176-235 (gelu), chosen as
+                    moe/sglang_moe_all_gather_all_reduce.py:374-397 does (intermediate
+                    rounded to out_dtype as the reference's gateup_output is)
       act quant 2   1x128 fp8 of the SwiGLU output
       GEMM-2        grouped blockwise GEMM with w2
       combine       moe/all2all_moe.py:270-278 (fp32 weighting and sum)
@@ -410,7 +432,8 @@ def moe_layer_fp8(x, topk_ids, topk_weight, w13, w13_s, w2, w2_s, *,
         widx = torch.arange(e0, e0 + E_l)
         gu = grouped_gemm_blockwise(a1[lo:hi], a1s[lo:hi], w13, w13_s, seg_r, widx, out_dtype)
         h = torch.empty(hi - lo, gu.shape[1] // 2, dtype=out_dtype, device=x.device)
-        silu_and_mul(gu, torch.zeros(hi - lo, dtype=torch.long), None, 0, 0, h)
+        act_mul = {"silu": silu_and_mul, "gelu": gelu_and_mul}[hidden_act]
+        act_mul(gu, torch.zeros(hi - lo, dtype=torch.long), None, 0, 0, h)
         hq, hs = act_quant_fp8(h)
         down_out[lo:hi] = grouped_gemm_blockwise(hq, hs, w2, w2_s, seg_r, widx, out_dtype)
     y = (down_out[src2dst.long()].view(T, k, H).float()
@@ -434,7 +457,7 @@ def _combine(down_out, src2dst, topk_weight, T, k, out_dtype):
 
 
 def moe_layer_w4a16(x, topk_ids, topk_weight, w13_q, w13_scale, w13_zero, w2_q, w2_scale, w2_zero,
-                    out_dtype=torch.bfloat16):
+                    out_dtype=torch.bfloat16, hidden_act: str = "silu"):
     """w4a16 layer: bf16 rows are permuted unquantized (moe/group_gemm_kernel.py:81-117); each
     expert multiplies by its dequantized int4 weights ((q - zero) * scale rounded to bf16, the
     zero-point extension of fast_dequant/simple_marlin/utils.py:98-136) with f32 accumulation;
@@ -453,13 +476,13 @@ def moe_layer_w4a16(x, topk_ids, topk_weight, w13_q, w13_scale, w13_zero, w2_q, 
         w13 = w4a16_dequant(w13_q[e], w13_scale[e], w13_zero[e]).float()
         gu = (a[m0:m1].float() @ w13.t()).to(out_dtype)
         h = torch.empty(m1 - m0, gu.shape[1] // 2, dtype=out_dtype, device=x.device)
-        silu_and_mul(gu, torch.zeros(m1 - m0, dtype=torch.long), None, 0, 0, h)
+        {"silu": silu_and_mul, "gelu": gelu_and_mul}[hidden_act](gu, torch.zeros(m1 - m0, dtype=torch.long), None, 0, 0, h)
         w2 = w4a16_dequant(w2_q[e], w2_scale[e], w2_zero[e]).float()
         down[m0:m1] = (h.float() @ w2.t()).to(out_dtype)
     return _combine(down, src2dst, topk_weight, T, k, out_dtype)
 
 
-def moe_layer_w4a8(x, topk_ids, topk_weight, w13, w2, out_dtype=torch.bfloat16):
+def moe_layer_w4a8(x, topk_ids, topk_weight, w13, w2, out_dtype=torch.bfloat16, hidden_act: str = "silu"):
     """w4a8 layer: tokens are quantized to int8 per 1x128 group (quantization/w4a8_kernel.py:145-193)
     before the permutation; each expert runs w4a8_gemm (:317-448) for gate/up, SwiGLU
     (moe/group_gemm_kernel.py:120-168), re-quantizes to int8, runs w4a8_gemm for down; f32
@@ -477,7 +500,7 @@ def moe_layer_w4a8(x, topk_ids, topk_weight, w13, w2, out_dtype=torch.bfloat16):
             continue
         gu = w4a8_gemm(a[m0:m1], a_s[m0:m1], *w13[e], out_dtype=out_dtype)
         h = torch.empty(m1 - m0, gu.shape[1] // 2, dtype=out_dtype, device=x.device)
-        silu_and_mul(gu, torch.zeros(m1 - m0, dtype=torch.long), None, 0, 0, h)
+        {"silu": silu_and_mul, "gelu": gelu_and_mul}[hidden_act](gu, torch.zeros(m1 - m0, dtype=torch.long), None, 0, 0, h)
         hq, hs = act_quant_int8(h, rounding="floor_half")
         down[m0:m1] = w4a8_gemm(hq, hs, *w2[e], out_dtype=out_dtype)
     return _combine(down, src2dst, topk_weight, T, k, out_dtype)

@@ -197,3 +197,31 @@ def test_marlin_mul_rejects_like_the_reference_binding():
         mul(A[:15], B, C[:15], s, None)
     with pytest.raises(RuntimeError, match="same CUDA device"):
         mul(A, B, C, s, None)                   # CPU tensors: there is no CPU path
+
+
+def test_operators_refuse_tensors_of_another_device(native, monkeypatch):
+    """require_cuda: a tensor that lives on a GPU other than the current one must raise before any launch
+    (the launchers use the current device's stream; a foreign pointer would be dereferenced on the wrong GPU)."""
+    from types import SimpleNamespace
+    monkeypatch.setattr(torch.cuda, "current_device", lambda: 0)
+    here = SimpleNamespace(is_cuda=True, device=SimpleNamespace(index=0))
+    there = SimpleNamespace(is_cuda=True, device=SimpleNamespace(index=1))
+    native.require_cuda(here, None, here)
+    with pytest.raises(RuntimeError, match="current device"):
+        native.require_cuda(here, there)
+
+
+def test_sglang_mirror_exports_grouped_gemm_runner():
+    """The reference's EPMoE builds `GroupedGemmRunner(device)` and calls it with grouped_gemm_triton's argument
+    order (moe/sglang_moe_all_gather_all_reduce.py:25-55); the mirror module exports the same class."""
+    import inspect
+    from llm_kernels_b200.moe import sglang_moe_all_gather_all_reduce as M
+    r = M.GroupedGemmRunner("cuda")
+    assert isinstance(r, torch.nn.Module) and r.use_flashinfer is False
+    names = list(inspect.signature(r.forward).parameters)
+    assert names == ["a", "b", "c", "batch_size", "weight_column_major", "seg_indptr", "weight_indices",
+                     "use_fp8_w8a8", "scale_a", "scale_b", "block_shape"]
+    with pytest.raises(RuntimeError):          # CPU tensors are refused like everywhere else
+        z = torch.zeros(2, 128, dtype=torch.float16)
+        r(z, torch.zeros(1, 128, 128, dtype=torch.float16), torch.zeros(2, 128, dtype=torch.float16), 1, True,
+          torch.tensor([0, 2]))

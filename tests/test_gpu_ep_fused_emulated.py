@@ -46,18 +46,32 @@ def test_fused_exchange_emulated(dev, ep, E, tokens, cap_factor):
     counts_all = torch.stack([m[2][1:] - m[2][:-1] for m in meta]).contiguous()          # [ep, E]
     plans = [G.ep_plan(counts_all.view(-1), r, ep, cap, recv_base, rec, back_base, Nout * 2) for r in range(ep)]
 
-    # ---- the plan against a host computation
+    # ---- the plan against a host computation.  Capacity rule on both sides: block (expert, source) is accepted
+    # iff it fits whole; accepted blocks are a prefix of the owner's buffer
     c = counts_all.cpu()
     overflow = False
+    valid = []                                             # rows each owner computes
+    rejected = torch.zeros(ep, E, dtype=torch.bool)        # [source, expert]
+    for d in range(ep):
+        run, first_bad = 0, None
+        for el in range(El):
+            for s_ in range(ep):
+                cnt = int(c[s_, d * El + el])
+                if cnt > 0 and run + cnt > cap:
+                    rejected[s_, d * El + el] = True
+                    first_bad = run if first_bad is None else first_bad
+                run += cnt
+        valid.append(run if first_bad is None else min(first_bad, cap))
+        overflow |= first_bad is not None
     for r in range(ep):
         dst_base, local_seg, back_addr, info = [t.cpu() for t in plans[r]]
         tot = c[:, r * El:(r + 1) * El].sum(0)
         seg = torch.zeros(El + 1, dtype=torch.int64)
         seg[1:] = torch.cumsum(tot, 0)
-        overflow |= int(seg[-1]) > cap
-        assert torch.equal(local_seg, seg.clamp(max=cap))
-        assert int(info[0]) == min(int(seg[-1]), cap)
-        assert bool(info[1]) == (int(seg[-1]) > cap) or bool(info[1])      # senders flag their own drops too
+        assert torch.equal(local_seg, seg.clamp(max=valid[r]))
+        assert int(info[0]) == valid[r]
+        assert bool(info[1]) == bool(valid[r] < int(seg[-1]) or rejected[r].any())
+        assert torch.equal((dst_base == 0) & (c[r] > 0), rejected[r])
     if cap_factor < 1.0:
         assert overflow and any(int(p[3][1].item()) for p in plans), "the overflow case must be flagged"
 
@@ -67,20 +81,19 @@ def test_fused_exchange_emulated(dev, ep, E, tokens, cap_factor):
         send = torch.zeros(max(tokens[r] * k, 1), rec, dtype=torch.uint8, device=dev)
         G.permute_quant_fp8(xs[r], meta[r][1], ids[r], 0, E - 1, send[:, :H], send[:, H:H + (H // 128) * 4].view(torch.float32))
         sends.append(send)
-        G.permute_quant_fp8_push(xs[r], meta[r][1], ids[r], meta[r][2], plans[r][0], rec)
+        G.permute_quant_fp8_push(xs[r], meta[r][1], ids[r], meta[r][2], plans[r][0], rec, back_local=back[r])
     torch.cuda.synchronize()
-    if overflow:
-        return      # memory safety and the flag are what this case checks
     segs = [m[2].cpu() for m in meta]
     for d in range(ep):
         want = [sends[s][int(segs[s][d * El + el]):int(segs[s][d * El + el + 1])] for el in range(El) for s in range(ep)]
         want = torch.cat(want) if want else recv[d][:0]
-        rows = want.shape[0]
-        assert rows == int(plans[d][3][0].item())
+        rows = valid[d]
+        assert rows == int(plans[d][3][0].item()) and rows <= want.shape[0]
         used = H + (H // 128) * 4
-        assert torch.equal(recv[d][:rows, :used], want[:, :used])
+        assert torch.equal(recv[d][:rows, :used], want[:rows, :used])
 
-    # ---- compute on the owners, results stored at their sources; against one GEMM per source rank
+    # ---- compute on the owners, results stored at their sources; against one GEMM per source rank.  Slots whose
+    # block was rejected get zeros back (cleared by the push kernel), never stale data
     for d in range(ep):
         a_q, a_s = recv[d][:, :H], recv[d][:, H:H + (H // 128) * 4].view(torch.float32)
         G.grouped_gemm_fp8(a_q, a_s, w[d * El:(d + 1) * El].contiguous(), w_s[d * El:(d + 1) * El].contiguous(),
@@ -94,4 +107,7 @@ def test_fused_exchange_emulated(dev, ep, E, tokens, cap_factor):
         G.grouped_gemm_fp8(sends[s][:n, :H], sends[s][:n, H:H + (H // 128) * 4].view(torch.float32), w, w_s,
                            meta[s][2], None, ref, None, epilogue=0)
         torch.cuda.synchronize()
+        dropped = rejected[s][meta[s][0].cpu()].to(dev)            # per sorted slot: its expert's block was rejected
+        ref[dropped] = 0
         assert torch.equal(back[s][:n], ref)
+        assert overflow or not bool(dropped.any())

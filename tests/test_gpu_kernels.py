@@ -69,6 +69,29 @@ def test_weight_quant_dequant_fp8(dev, shape):
     assert torch.equal(d.cpu(), R.weight_dequant_fp8(qo, so))
 
 
+@pytest.mark.parametrize("shape", [(128, 128), (200, 300), (512, 1024), (7168, 256)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_weight_quant_dequant_int8_bit_exact(dev, shape, dtype):
+    """int8_kernel.weight_quant / weight_dequant (reference quantization/int8_kernel.py:91-113, 145-170):
+    int8 payload, f16 scales and the dequantized weight must equal the oracle bit for bit, edge blocks
+    and a half-way value included."""
+    from llm_kernels_b200.quantization import int8_kernel
+    g = torch.Generator().manual_seed(7)
+    w = (torch.randn(*shape, generator=g) * 0.01).to(dtype)
+    w[0, 0] = w[:128, :128].abs().max() * (2.5 / 127.0)          # lands on a rounding tie
+    q, s = int8_kernel.weight_quant(w.to(dev))
+    qo, so = R.weight_quant_int8(w)
+    assert s.dtype == torch.float16 and s.shape == so.shape and torch.equal(s.cpu(), so)
+    assert q.dtype == torch.int8 and torch.equal(q.cpu(), qo)
+    old = torch.get_default_dtype()
+    try:
+        torch.set_default_dtype(torch.float32)
+        d = int8_kernel.weight_dequant(q, s)
+    finally:
+        torch.set_default_dtype(old)
+    assert torch.equal(d.cpu(), R.weight_dequant_int8(qo, so))
+
+
 @pytest.mark.parametrize("rounding", ["half_away", "floor_half"])
 def test_act_quant_int8_bit_exact(dev, rounding):
     from llm_kernels_b200.quantization import int8_kernel
@@ -373,20 +396,40 @@ def test_grouped_gemm_triton_surface(dev):
     assert R.rel_fro(c.cpu().float(), ref) < 3e-3
 
 
+def test_grouped_gemm_runner_surface(dev):
+    """GroupedGemmRunner(device).forward(...) (reference moe/sglang_moe_all_gather_all_reduce.py:25-55) gives what
+    grouped_gemm_triton gives for the same arguments."""
+    from llm_kernels_b200.moe.sglang_moe_all_gather_all_reduce import GroupedGemmRunner
+    from llm_kernels_b200.moe.group_gemm_kernel import grouped_gemm_triton
+    g = torch.Generator().manual_seed(9)
+    a = torch.randn(100, 256, generator=g).to(torch.float16).to(dev)
+    b = (torch.randn(3, 128, 256, generator=g) * 0.05).to(torch.float16).to(dev)
+    seg = torch.tensor([0, 40, 40, 100], dtype=torch.int64, device=dev)
+    widx = torch.arange(3, dtype=torch.int64, device=dev)
+    c1 = torch.zeros(100, 128, dtype=torch.float16, device=dev)
+    c2 = torch.zeros_like(c1)
+    out = GroupedGemmRunner(dev)(a, b, c1, 3, True, seg, widx)
+    grouped_gemm_triton(a, b, c2, 3, True, seg, widx)
+    assert out is c1 and torch.equal(c1, c2)
+    ref = R.grouped_gemm_plain(a.cpu(), b.cpu(), seg.cpu(), widx.cpu(), out_dtype=torch.float32)
+    assert R.rel_fro(c1.cpu().float(), ref) < 2e-3
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
 @pytest.mark.parametrize("counts,I,K,W", [([5, 0, 65, 27], 128, 256, 4), ([200, 130], 256, 512, 2),
                                           ([33] * 8, 384, 1024, 8)])
-def test_grouped_gemm_fp8_swiglu_epilogue(dev, counts, I, K, W):
+def test_grouped_gemm_fp8_swiglu_epilogue(dev, counts, I, K, W, act):
     from llm_kernels_b200.moe import group_gemm_kernel as G
     aq, a_s, bq, b_s, seg, wi = _grouped_case(31, counts, 2 * I, K, W)
     M = aq.shape[0]
     hq = torch.zeros(M, I, dtype=torch.uint8, device=dev)
     hs = torch.zeros(M, I // 128, dtype=torch.float32, device=dev)
     G.grouped_gemm_fp8(aq.to(dev), a_s.to(dev), bq.to(dev), b_s.to(dev), seg.to(dev), wi.to(dev), hq, hs,
-                       epilogue=1)
+                       epilogue=1 if act == "silu" else 4)
     torch.cuda.synchronize()
     gu = R.grouped_gemm_blockwise(aq, a_s, bq, b_s, seg, wi, out_dtype=torch.bfloat16)
     h = torch.empty(M, I, dtype=torch.bfloat16)
-    R.silu_and_mul(gu, torch.zeros(M, dtype=torch.long), None, 0, 0, h)
+    (R.silu_and_mul if act == "silu" else R.gelu_and_mul)(gu, torch.zeros(M, dtype=torch.long), None, 0, 0, h)
     ho, so = R.act_quant_fp8(h)
     got = hq.cpu().view(torch.float8_e4m3fn).float() * hs.cpu().repeat_interleave(128, 1)
     want = ho.float() * so.repeat_interleave(128, 1)
@@ -471,4 +514,7 @@ def test_grouped_gemm_bf16_plain_and_swiglu(dev, counts, I, K, W):
     G.grouped_gemm_bf16(a.to(dev), b.to(dev), seg.to(dev), None, h, epilogue=2)
     want = torch.empty(M, I, dtype=torch.bfloat16)
     R.silu_and_mul(ref.to(torch.bfloat16), torch.zeros(M, dtype=torch.long), None, 0, 0, want)
+    assert R.rel_fro(h.cpu().float(), want.float()) < 3e-3
+    G.grouped_gemm_bf16(a.to(dev), b.to(dev), seg.to(dev), None, h, epilogue=5)       # GELU(gate) * up
+    R.gelu_and_mul(ref.to(torch.bfloat16), torch.zeros(M, dtype=torch.long), None, 0, 0, want)
     assert R.rel_fro(h.cpu().float(), want.float()) < 3e-3

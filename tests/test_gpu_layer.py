@@ -7,7 +7,7 @@ from oracle import restate as R
 pytestmark = pytest.mark.gpu
 
 
-def _oracle_layer(shape, x, ep_size=1):
+def _oracle_layer(shape, x, ep_size=1, hidden_act="silu"):
     from llm_kernels_b200 import workloads as WL
     W, bias = WL.router_params(shape)
     kw = dict(top_k=shape.top_k, n_group=shape.n_group, topk_group=shape.topk_group,
@@ -22,14 +22,16 @@ def _oracle_layer(shape, x, ep_size=1):
         q2.append(R.weight_quant_fp8(d))
     w13 = torch.stack([a for a, _ in q13]); w13s = torch.stack([s for _, s in q13])
     w2 = torch.stack([a for a, _ in q2]); w2s = torch.stack([s for _, s in q2])
-    y = R.moe_layer_fp8(x, idx, w, w13, w13s, w2, w2s, ep_size=ep_size)
+    y = R.moe_layer_fp8(x, idx, w, w13, w13s, w2, w2s, ep_size=ep_size, hidden_act=hidden_act)
     return idx, w, y, (w13, w13s, w2, w2s)
 
 
-def _build_layer(shape, dev):
+def _build_layer(shape, dev, hidden_act="silu"):
     from llm_kernels_b200 import workloads as WL
     from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
-    layer = DeepseekV3MoE(WL.make_config(shape), device=dev).eval()
+    cfg = WL.make_config(shape)
+    cfg.hidden_act = hidden_act
+    layer = DeepseekV3MoE(cfg, device=dev).eval()
     WL.fill_layer_cpu_seeded(layer, shape)
     return layer
 
@@ -55,6 +57,39 @@ def test_layer_config0_matches_oracle():
     assert y.shape == (2, 256, shape.hidden) and y.dtype == torch.bfloat16
     err = R.rel_fro(y.cpu().view(-1, shape.hidden).float(), y_ref.float())
     assert err < 1e-2, err
+
+
+def test_layer_gelu_activation_matches_oracle():
+    """config.hidden_act = "gelu" (the activation switch of reference
+    moe/sglang_moe_all_gather_all_reduce.py:374-397): the tanh-GELU of gelu_and_mul_triton_kernel fused into the
+    GEMM-1 epilogue, fp8 and w4a16 paths, against the oracle with the same activation."""
+    from llm_kernels_b200 import workloads as WL
+    from dataclasses import replace
+    dev = torch.device("cuda:0")
+    shape = replace(WL.CONFIG0, tokens=160, hidden=512, inter=256, seed=61)
+    x = WL.tokens(shape)
+    _, _, y_ref, _ = _oracle_layer(shape, x, hidden_act="gelu")
+    _, _, y_silu, _ = _oracle_layer(shape, x)
+    assert R.rel_fro(y_ref.float(), y_silu.float()) > 0.05          # the two activations differ visibly here
+    layer = _build_layer(shape, dev, hidden_act="gelu")
+    y = layer(x.to(dev).view(1, shape.tokens, -1))
+    layer.check_status()
+    assert R.rel_fro(y.cpu().view(shape.tokens, -1).float(), y_ref.float()) < 1e-2
+    # w4a16 path (bf16 GEMM-1 with the GELU epilogue)
+    shape2 = replace(WL.CONFIG2, tokens=120, hidden=512, inter=256)
+    x2, idx, w = _seeded_router_and_tokens(shape2)
+    qs = [[], [], [], [], [], []]
+    for e in range(shape2.experts):
+        g, u, d = WL.expert_weights_cpu(shape2, e)
+        q, s_, z = R.w4a16_quantize_asym(torch.cat([g, u], 0))
+        qs[0].append(q); qs[1].append(s_); qs[2].append(z)
+        q, s_, z = R.w4a16_quantize_asym(d)
+        qs[3].append(q); qs[4].append(s_); qs[5].append(z)
+    y_ref2 = R.moe_layer_w4a16(x2, idx, w, *[torch.stack(v) for v in qs], hidden_act="gelu")
+    layer2 = _build_layer(shape2, dev, hidden_act="gelu")
+    y2 = layer2.triton_group_gemm_moe_infer(x2.to(dev), idx.to(dev), w.to(dev))
+    layer2.check_status()
+    assert R.rel_fro(y2.cpu().float(), y_ref2.float()) < 3e-3
 
 
 @pytest.mark.parametrize("T", [1, 3, 127, 129])

@@ -151,6 +151,19 @@ def test_weight_quant_fp8_roundtrip():
     assert float(q.float().abs().max()) == 448.0
 
 
+def test_weight_quant_int8_roundtrip_and_ties():
+    """Formula pin of int8_kernel.weight_quant (the Triton kernel needs libdevice): scale = amax/127,
+    ties round away from zero, the block's extreme value maps to +-127, edge blocks are masked."""
+    g = torch.Generator().manual_seed(6)
+    w = torch.randn(200, 300, generator=g) * 0.02
+    w[0, 0] = w[:128, :128].abs().max()
+    w[1, 0], w[2, 0] = w[0, 0] * (2.5 / 127.0), -w[0, 0] * (2.5 / 127.0)
+    q, s = R.weight_quant_int8(w)
+    assert q.shape == w.shape and q.dtype == torch.int8 and s.shape == (2, 3) and s.dtype == torch.float16
+    assert int(q[0, 0]) == 127 and int(q[1, 0]) == 3 and int(q[2, 0]) == -3
+    assert R.rel_fro(R.weight_dequant_int8(q, s), w) < 0.02
+
+
 @pytest.mark.parametrize("nbits,width", [(4, 32), (4, 8), (2, 16), (8, 32), (1, 8)])
 def test_bitpack(golden, nbits, width):
     c = golden.case(f"bitpack_{nbits}_{width}")
