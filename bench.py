@@ -220,18 +220,18 @@ def bind_to_gpu_numa_node(dev):
         bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
         node = int(open(f"/sys/bus/pci/devices/{bdf}/numa_node").read())
         if node < 0:
-            return None
+            return "single node (no NUMA affinity reported for the GPU)"
         cpus = set()
         for part in open(f"/sys/devices/system/node/node{node}/cpulist").read().strip().split(","):
             lo, _, hi = part.partition("-")
             cpus.update(range(int(lo), int(hi or lo) + 1))
         allowed = cpus & os.sched_getaffinity(0)
         if not allowed:
-            return None
+            return f"node{node}: none of its CPUs is in this process's affinity mask"
         os.sched_setaffinity(0, allowed)
         return f"node{node}:{len(allowed)}cpus"
-    except Exception:
-        return None
+    except Exception as e:
+        return f"not bound ({type(e).__name__})"
 
 
 def parity_check(world, rank, dev, exchange):

@@ -116,6 +116,18 @@ B200MOE_API int b200moe_weight_quant_int8(const void* w, int w_dtype, void* y_in
 B200MOE_API int b200moe_weight_dequant_int8(const void* x_int8, const void* s_f16, void* y, int y_dtype,
                                 int64_t M, int64_t N, void* stream);
 
+/* Middle step of the quantized all-reduce (quant_communication/quant_all2all_allreduce.py:73-80): the chunks
+ * received from n_src ranks -- payload q (e4m3 with f32 scales, or int8 with f16 scales; one scale per 128
+ * values of a row), source `i` at q + i * q_src_stride_bytes and s + i * s_src_stride (elements) -- are
+ * dequantized (product formed in the scales' dtype as the reference's dequant kernels do,
+ * quant_communication/quant_utils.py:75-83, 176-180, then cast to out_dtype), summed in f32 in source order and
+ * the sum is rounded to out_dtype (bf16/f16).  A group whose scale is 0 (all-zero input, whose payload is
+ * NaN by the quantizers' x / s) decodes to zero.  With n_src == 1 this is the plain dequantization of the
+ * all-gather step (:96-99).  cols % 128 == 0. */
+B200MOE_API int b200moe_dequant_sum(const void* q, int q_dtype, int64_t q_row_stride_bytes, int64_t q_src_stride_bytes,
+                        const void* s, int s_dtype, int64_t s_row_stride, int64_t s_src_stride, int n_src,
+                        int64_t rows, int64_t cols, void* out, int out_dtype, void* stream);
+
 /* ========================= moe/all2all_moe.py ============================= */
 
 /* MoEGate.forward (moe/all2all_moe.py:60-118).
@@ -241,6 +253,17 @@ B200MOE_API int b200moe_post_reorder(const void* down_output, int dtype, void* o
                          const float* topk_weights, int start_expert_id, int end_expert_id,
                          int64_t T, int topk, int64_t H, void* stream);
 
+/* Per-call launch options of the grouped tcgen05 GEMMs (a NULL pointer means all zeros).  No counterpart in the
+ * reference (its Triton grids are sized by the tile count, moe/group_gemm_kernel.py:484-487).
+ *   max_ctas   upper bound on the persistent grid; 0 = one CTA per SM.  A GEMM CTA owns its whole SM, so a
+ *              collective that is meant to run beside the GEMM only progresses if some SMs are left free.
+ *   pair_mode  0 = one CTA per 128 x 256 tile; 1 = clusters of two CTAs sharing a 256 x 256 tile (tcgen05
+ *              cta_group::2: each SM then moves 32 KB instead of 48 KB per K block).  Results are identical. */
+typedef struct b200moe_gemm_opts {
+  int32_t max_ctas;
+  int32_t pair_mode;
+} b200moe_gemm_opts;
+
 /* grouped_gemm_triton with block_shape = [128,128]
  * (moe/group_gemm_kernel.py:442-513; kernel :291-428), fp8 operands.
  * For every group g, rows [seg_indptr[g], seg_indptr[g+1]) of a use weight
@@ -279,19 +302,7 @@ B200MOE_API int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byt
                              int num_groups, int num_weights,
                              const int64_t* seg_indptr, const int64_t* weight_indices,
                              int epilogue, const int32_t* c_row_map, const int64_t* c_row_addr,
-                             int32_t* status_word, void* stream);
-
-/* Caps the grid of the persistent tcgen05 GEMM kernels of this process (0 = one CTA per SM,
- * the default).  A GEMM CTA owns its whole SM, so an NCCL kernel that is meant to overlap the
- * GEMM only makes progress if some SMs are left free.  No counterpart in the reference (its
- * Triton grids are sized by the tile count, moe/group_gemm_kernel.py:484-487). */
-B200MOE_API int b200moe_set_gemm_max_ctas(int max_ctas);
-
-/* No counterpart in the reference.  Tile shape of the grouped/dense GEMMs above: 0 = one CTA per
- * 128 x 256 tile, 1 = clusters of two CTAs sharing a 256 x 256 tile (tcgen05 cta_group::2; each
- * SM then moves 32 KB instead of 48 KB per K block through the crossbar).  Default 0: measured
- * within +-5 % of single-CTA tiles for every kind.  Results are identical in both modes. */
-B200MOE_API int b200moe_set_gemm_pair_mode(int mode);
+                             int32_t* status_word, const b200moe_gemm_opts* opts, void* stream);
 
 /* ===================== int4 weight paths (w4a8, w4a16) ==================== */
 
@@ -339,7 +350,7 @@ B200MOE_API int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_byte
                             int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                             int64_t K, int num_groups, int num_weights,
                             const int64_t* seg_indptr, const int64_t* weight_indices,
-                            int32_t* status_word, void* stream);
+                            int32_t* status_word, const b200moe_gemm_opts* opts, void* stream);
 
 /* Grouped bf16 x bf16 GEMM with f32 accumulation in TMEM (the unquantized branch of
  * grouped_gemm_triton, moe/group_gemm_kernel.py:410-412; used by the w4a16 path after
@@ -354,7 +365,7 @@ B200MOE_API int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_by
                               int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                               int64_t K, int num_groups, int num_weights,
                               const int64_t* seg_indptr, const int64_t* weight_indices,
-                              int epilogue, int32_t* status_word, void* stream);
+                              int epilogue, int32_t* status_word, const b200moe_gemm_opts* opts, void* stream);
 
 /* Same with f16 operands (plain epilogue only): the matrix product of the reference's w4a16
  * `mul` (fast_dequant/simple_marlin/marlin_w4a16_gemm.cpp:23-111) after
@@ -363,7 +374,7 @@ B200MOE_API int b200moe_grouped_gemm_f16(const void* a, int64_t a_row_stride_byt
                              int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                              int64_t K, int num_groups, int num_weights,
                              const int64_t* seg_indptr, const int64_t* weight_indices,
-                             int32_t* status_word, void* stream);
+                             int32_t* status_word, const b200moe_gemm_opts* opts, void* stream);
 
 /* Expands Marlin-order symmetric int4 weights (QuantUtils.pack,
  * fast_dequant/simple_marlin/utils.py:53-95; dequantization of

@@ -34,6 +34,7 @@ SIGNATURES = {
     "b200moe_gemm_fp8_block": (_i, [_p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _p]),
     "b200moe_gemm_fp8_block_splitk": (_i, [_p, _p, _p, _p, _p, _i, _i64, _i64, _i64, _i, _p, _i64, _p]),
     "b200moe_act_quant_int8": (_i, [_p, _i, _i64, _i64, _p, _p, _i, _p]),
+    "b200moe_dequant_sum": (_i, [_p, _i, _i64, _i64, _p, _i, _i64, _i64, _i, _i64, _i64, _p, _i, _p]),
     "b200moe_router_topk": (_i, [_p, _i, _p, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p]),
     "b200moe_router_logits_bf16x3": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
     "b200moe_router_select": (_i, [_p, _i, _p, _i64, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p]),
@@ -46,19 +47,17 @@ SIGNATURES = {
     "b200moe_act_and_mul": (_i, [_p, _i, _p, _i, _i64, _i64, _p, _p, _i, _i, _i, _p]),
     "b200moe_post_reorder": (_i, [_p, _i, _p, _p, _p, _p, _i, _i, _i64, _i, _i64, _p]),
     "b200moe_grouped_gemm_fp8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _p, _i64,
-                                      _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p, _p]),
+                                      _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p, _p, _p]),
     "b200moe_ep_plan_workspace_bytes": (_i64, [_i, _i]),
     "b200moe_ep_plan": (_i, [_p, _i, _i, _i, _i64, _p, _i64, _p, _i64, _p, _p, _p, _p, _p, _i64, _p]),
     "b200moe_permute_quant_fp8_push": (_i, [_p, _i, _p, _p, _p, _p, _i, _i64, _i, _i64, _i64, _p, _i64, _p]),
     "b200moe_gather_rows": (_i, [_p, _p, _p, _i64, _i64, _p]),
-    "b200moe_set_gemm_max_ctas": (_i, [_i]),
-    "b200moe_set_gemm_pair_mode": (_i, [_i]),
     "b200moe_w4a8_expand_int8": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "b200moe_w4a16_expand_bf16": (_i, [_p, _p, _p, _p, _i64, _i64, _p]),
     "b200moe_grouped_gemm_i8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i,
-                                     _p, _p, _p, _p]),
-    "b200moe_grouped_gemm_bf16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p]),
-    "b200moe_grouped_gemm_f16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p]),
+                                     _p, _p, _p, _p, _p]),
+    "b200moe_grouped_gemm_bf16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p]),
+    "b200moe_grouped_gemm_f16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p, _p]),
     "b200moe_marlin_expand_f16": (_i, [_p, _p, _p, _i64, _i64, _i64, _p]),
     "b200moe_marlin_pack": (_i, [_p, _p, _p, _p, _i64, _i64, _i64, _p]),
     "b200moe_weight_quant_int8": (_i, [_p, _i, _p, _p, _i64, _i64, _f, _i, _p]),
@@ -68,6 +67,11 @@ SIGNATURES = {
     "b200moe_pack_bits": (_i, [_p, _p, _i64, _i64, _i, _i, _i, _p]),
     "b200moe_unpack_bits": (_i, [_p, _p, _i64, _i64, _i, _i, _i, _p]),
 }
+
+class GemmOpts(C.Structure):
+    """b200moe_gemm_opts: per-call launch options of the grouped GEMMs."""
+    _fields_ = [("max_ctas", C.c_int32), ("pair_mode", C.c_int32)]
+
 
 _lib = None
 _lock = threading.Lock()

@@ -41,6 +41,6 @@ const char* b200moe_status_string(int status) {
 
 const char* b200moe_last_error(void) { return b200moe::g_last_error; }
 
-int b200moe_abi_version(void) { return 1; }
+int b200moe_abi_version(void) { return 2; }
 
 }  // extern "C"

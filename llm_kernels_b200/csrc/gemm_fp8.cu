@@ -628,17 +628,6 @@ gemm_block_kernel(const __grid_constant__ RowMaps tmap_a,
 }
 
 // ---- host side ---------------------------------------------------------------------------
-// Upper bound on the persistent grid (0 = one CTA per SM).  A GEMM CTA takes a whole SM
-// (registers and shared memory), so a collective that should run concurrently needs SMs left free.
-static int g_max_ctas = 0;
-// CTA pairs (256-row tiles): 0 = off (default), 1 = on.  Measured on B200 with 32 groups x 1024
-// rows: bf16/f16 operands gain 5 % from pairs; the kinds that promote every K block come out within
-// 3 % of single-CTA tiles either way (they are bound by the tensor-memory read-back, not by the
-// 48 KB vs 32 KB per K block that pairs save), once the peer's stage hand-over is a RELAXED
-// cluster-scope arrive: as a release it waited for the thread's earlier global stores and loads
-// and halved the throughput.
-static int g_pair_mode = 0;
-
 template <int KIND, bool PAIR>
 static int launch_gemm_as(const RowMaps& ma, const CUtensorMap& mb, const GemmParams& p, int grid, cudaStream_t st) {
   cudaFuncSetAttribute(gemm_block_kernel<KIND, PAIR>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -660,24 +649,29 @@ static int launch_gemm_as(const RowMaps& ma, const CUtensorMap& mb, const GemmPa
   return check_launch("gemm_block_kernel");
 }
 
+// opts (may be null): per-call launch options of the grouped GEMMs (b200moe_gemm_opts).
 template <int KIND>
 static int launch_gemm(const void* a, int64_t a_stride, const void* b, GemmParams p, int64_t tiles_hint,
-                       cudaStream_t st) {
+                       cudaStream_t st, const b200moe_gemm_opts* opts = nullptr) {
+  const int max_ctas = opts ? opts->max_ctas : 0;
+  const int pair_mode = opts ? opts->pair_mode : 0;
+  B200MOE_REQUIRE(max_ctas >= 0 && (pair_mode == 0 || pair_mode == 1), B200MOE_BAD_ARG,
+                  "gemm options: max_ctas %d, pair_mode %d", max_ctas, pair_mode);
   int sms = 0;
   if (int rc = require_sm100(&sms)) return rc;
   RowMaps ma;
   CUtensorMap mb;
   for (int i = 0; i < 4; ++i)
-    if (int rc = make_tensor_map_u8(&ma.m[i], a, static_cast<uint64_t>(p.M_total),
+    if (int rc = cached_tensor_map_u8(&ma.m[i], a, static_cast<uint64_t>(p.M_total),
                                     static_cast<uint64_t>(p.a_wrap ? p.a_wrap : p.K),
                                     static_cast<uint64_t>(a_stride), 16u << i)) return rc;
-  if (int rc = make_tensor_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K),
+  if (int rc = cached_tensor_map_u8(&mb, b, static_cast<uint64_t>(p.num_weights) * p.N, static_cast<uint64_t>(p.K),
                                   static_cast<uint64_t>(p.K), 128)) return rc;
   int grid = sms;
-  if (g_max_ctas > 0 && g_max_ctas < grid) grid = g_max_ctas;
+  if (max_ctas > 0 && max_ctas < grid) grid = max_ctas;
   if (tiles_hint > 0 && tiles_hint < grid) grid = static_cast<int>(tiles_hint);
   // N must cover both halves of a pair's tile; split-K launches stay single.
-  bool pair = g_pair_mode == 1;
+  bool pair = pair_mode == 1;
   if (p.ksplits > 1 || grid < 2 || (!p.swiglu && p.N % BN != 0)) pair = false;
   if (pair) return launch_gemm_as<KIND, true>(ma, mb, p, grid & ~1, st);
   return launch_gemm_as<KIND, false>(ma, mb, p, grid, st);
@@ -770,7 +764,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
                                         int num_groups, int num_weights, const int64_t* seg_indptr,
                                         const int64_t* weight_indices, int epilogue,
                                         const int32_t* c_row_map, const int64_t* c_row_addr,
-                                        int32_t* status_word, void* stream) {
+                                        int32_t* status_word, const b200moe_gemm_opts* opts, void* stream) {
   B200MOE_REQUIRE(a && a_s && b && b_s && c && seg_indptr, B200MOE_BAD_ARG, "grouped_gemm_fp8: null pointer");
   B200MOE_REQUIRE((c_row_map == nullptr && c_row_addr == nullptr) || epilogue == 0, B200MOE_BAD_ARG,
                   "grouped_gemm_fp8: c_row_map / c_row_addr need epilogue 0");
@@ -801,7 +795,7 @@ extern "C" int b200moe_grouped_gemm_fp8(const void* a, int64_t a_row_stride_byte
                weight_indices, M_total, static_cast<int>(N), static_cast<int>(K), num_groups,
                num_weights, c_dtype, epilogue == 4 ? 1 : epilogue, status_word, 1, 0, 0, c_row_map, c_row_addr, 0,
                epilogue == 4 ? 1 : 0};
-  return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+  return launch_gemm<kFp8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream), opts);
 }
 
 // ---- int8 x int8 (w4a8 after the int4 -> int8 step) and bf16 x bf16 (w4a16 after dequantization) ----
@@ -825,7 +819,7 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
                                        int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                                        int64_t K, int num_groups, int num_weights,
                                        const int64_t* seg_indptr, const int64_t* weight_indices,
-                                       int32_t* status_word, void* stream) {
+                                       int32_t* status_word, const b200moe_gemm_opts* opts, void* stream) {
   if (int rc = check_grouped_common("grouped_gemm_i8", a, b, c, seg_indptr, a_row_stride_bytes, K, M_total, N,
                                     num_groups, num_weights)) return rc;
   B200MOE_REQUIRE(a_s && b_s && a_s_row_stride >= K / 128, B200MOE_BAD_ARG, "grouped_gemm_i8: scales");
@@ -836,14 +830,14 @@ extern "C" int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_bytes
   if (M_total == 0) return B200MOE_OK;
   GemmParams p{a_s, a_s_row_stride, b_s, c, c_row_stride_bytes, nullptr, 0, seg_indptr, weight_indices, M_total,
                static_cast<int>(N), static_cast<int>(K), num_groups, num_weights, c_dtype, 0, status_word, 1, 0, 0, nullptr, nullptr, 0, 0};
-  return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+  return launch_gemm<kI8>(a, a_row_stride_bytes, b, p, 0, as_stream(stream), opts);
 }
 
 static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
                               int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                               int64_t K, int num_groups, int num_weights,
                               const int64_t* seg_indptr, const int64_t* weight_indices,
-                              int epilogue, int32_t* status_word, void* stream) {
+                              int epilogue, int32_t* status_word, const b200moe_gemm_opts* opts, void* stream) {
   if (int rc = check_grouped_common("grouped_gemm_bf16", a, b, c, seg_indptr, a_row_stride_bytes, 2 * K, M_total, N,
                                     num_groups, num_weights)) return rc;
   B200MOE_REQUIRE(epilogue == 0 || epilogue == 3 || ((epilogue == 2 || epilogue == 5) && !f16), B200MOE_BAD_ARG,
@@ -864,26 +858,27 @@ static int grouped_gemm_16bit(bool f16, const void* a, int64_t a_row_stride_byte
                static_cast<int>(N), static_cast<int>(2 * K), num_groups, num_weights, c_dtype,
                epilogue == 3 ? 0 : (epilogue == 5 ? 2 : epilogue), status_word, 1, 0, 0, nullptr, nullptr,
                epilogue == 3 ? 1 : 0, epilogue == 5 ? 1 : 0};
-  return f16 ? launch_gemm<kF16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream))
-             : launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream));
+  return f16 ? launch_gemm<kF16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream), opts)
+             : launch_gemm<kBf16>(a, a_row_stride_bytes, b, p, 0, as_stream(stream), opts);
 }
 
 extern "C" int b200moe_grouped_gemm_bf16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
                                          int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                                          int64_t K, int num_groups, int num_weights,
                                          const int64_t* seg_indptr, const int64_t* weight_indices,
-                                         int epilogue, int32_t* status_word, void* stream) {
+                                         int epilogue, int32_t* status_word, const b200moe_gemm_opts* opts,
+                                         void* stream) {
   return grouped_gemm_16bit(false, a, a_row_stride_bytes, b, c, c_dtype, c_row_stride_bytes, M_total, N, K,
-                            num_groups, num_weights, seg_indptr, weight_indices, epilogue, status_word, stream);
+                            num_groups, num_weights, seg_indptr, weight_indices, epilogue, status_word, opts, stream);
 }
 
 extern "C" int b200moe_grouped_gemm_f16(const void* a, int64_t a_row_stride_bytes, const void* b, void* c,
                                         int c_dtype, int64_t c_row_stride_bytes, int64_t M_total, int64_t N,
                                         int64_t K, int num_groups, int num_weights,
                                         const int64_t* seg_indptr, const int64_t* weight_indices,
-                                        int32_t* status_word, void* stream) {
+                                        int32_t* status_word, const b200moe_gemm_opts* opts, void* stream) {
   return grouped_gemm_16bit(true, a, a_row_stride_bytes, b, c, c_dtype, c_row_stride_bytes, M_total, N, K,
-                            num_groups, num_weights, seg_indptr, weight_indices, 0, status_word, stream);
+                            num_groups, num_weights, seg_indptr, weight_indices, 0, status_word, opts, stream);
 }
 
 // ---- router logits on the tensor cores ------------------------------------------------------
@@ -908,16 +903,4 @@ extern "C" int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_b
                static_cast<int>(H * 2), nullptr, nullptr, 0, 0};
   const int64_t tiles = ((T + BM - 1) / BM) * ((E + BN - 1) / BN) * ksplits;
   return launch_gemm<kBf16>(x_bf16, H * 2, w3_bf16, p, tiles, as_stream(stream));
-}
-
-extern "C" int b200moe_set_gemm_pair_mode(int mode) {
-  B200MOE_REQUIRE(mode == 0 || mode == 1, B200MOE_BAD_ARG, "set_gemm_pair_mode: %d (0 off, 1 on)", mode);
-  g_pair_mode = mode;
-  return B200MOE_OK;
-}
-
-extern "C" int b200moe_set_gemm_max_ctas(int max_ctas) {
-  B200MOE_REQUIRE(max_ctas >= 0, B200MOE_BAD_ARG, "set_gemm_max_ctas: %d", max_ctas);
-  g_max_ctas = max_ctas;
-  return B200MOE_OK;
 }

@@ -117,9 +117,65 @@ __global__ void __launch_bounds__(256) act_quant_int8_kernel(
   }
 }
 
+// Quantized all-reduce, middle step (quant_communication/quant_all2all_allreduce.py:73-80): the chunks received
+// from the n_src ranks are dequantized, each rounded to the output dtype, summed in f32 in rank order and the
+// sum rounded to the output dtype.  One thread owns 8 consecutive values of a row.
+template <typename TO, typename TS, bool FP8>
+__global__ void __launch_bounds__(256) dequant_sum_kernel(
+    const uint8_t* __restrict__ q, int64_t q_row_stride, int64_t q_src_stride, const TS* __restrict__ s,
+    int64_t s_row_stride, int64_t s_src_stride, int n_src, int64_t rows, int64_t cols, TO* __restrict__ out) {
+  const int64_t chunks = cols / 8, total = rows * chunks;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / chunks, c = (i - r * chunks) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int src = 0; src < n_src; ++src) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(q + src * q_src_stride + r * q_row_stride + c);
+      const float sc = static_cast<float>(s[src * s_src_stride + r * s_row_stride + c / 128]);
+      const uint8_t* b = reinterpret_cast<const uint8_t*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        // an all-zero group has scale 0 and, by the quantizer's x / s, a NaN payload: it decodes to zero
+        const float v = sc == 0.f ? 0.f : (FP8 ? e4m3_to_float(b[k]) : static_cast<float>(static_cast<int8_t>(b[k])));
+        // the product is formed in the scale's dtype (exact in f32, then one rounding), then cast to the output dtype
+        acc[k] += round_to(round_to(v * sc, TS()), TO());
+      }
+    }
+    store8(out + r * cols + c, acc);
+  }
+}
+
 }  // namespace b200moe
 
 using namespace b200moe;
+
+extern "C" int b200moe_dequant_sum(const void* q, int q_dtype, int64_t q_row_stride_bytes, int64_t q_src_stride_bytes,
+                                   const void* s, int s_dtype, int64_t s_row_stride, int64_t s_src_stride, int n_src,
+                                   int64_t rows, int64_t cols, void* out, int out_dtype, void* stream) {
+  B200MOE_REQUIRE(q && s && out, B200MOE_BAD_ARG, "dequant_sum: null pointer");
+  B200MOE_REQUIRE(rows >= 0 && cols >= 0 && cols % 128 == 0 && n_src >= 1, B200MOE_BAD_SHAPE,
+                  "dequant_sum: Last dimension size must be divisible by block_size (block_size=128), got %lld (%d sources)",
+                  (long long)cols, n_src);
+  B200MOE_REQUIRE((q_dtype == B200MOE_FP8_E4M3 && s_dtype == B200MOE_F32) || (q_dtype == B200MOE_I8 && s_dtype == B200MOE_F16),
+                  B200MOE_BAD_DTYPE, "dequant_sum: payload %d with scales %d (e4m3 + f32 or int8 + f16)", q_dtype, s_dtype);
+  B200MOE_REQUIRE(out_dtype == B200MOE_BF16 || out_dtype == B200MOE_F16, B200MOE_BAD_DTYPE, "dequant_sum: out dtype %d", out_dtype);
+  B200MOE_REQUIRE(aligned(q, 8) && q_row_stride_bytes % 8 == 0 && q_src_stride_bytes % 8 == 0 && aligned(out, 16),
+                  B200MOE_BAD_ALIGN, "dequant_sum: alignment");
+  B200MOE_REQUIRE(q_row_stride_bytes >= cols && s_row_stride >= cols / 128, B200MOE_BAD_ARG, "dequant_sum: strides smaller than a row");
+  if (rows == 0 || cols == 0) return B200MOE_OK;
+  const unsigned grid = static_cast<unsigned>(std::min<int64_t>((rows * (cols / 8) + 255) / 256, 148 * 16));
+  cudaStream_t st = as_stream(stream);
+  const uint8_t* q8 = static_cast<const uint8_t*>(q);
+#define DQS(TO, TS, F8) dequant_sum_kernel<TO, TS, F8><<<grid, 256, 0, st>>>(q8, q_row_stride_bytes, q_src_stride_bytes, \
+    static_cast<const TS*>(s), s_row_stride, s_src_stride, n_src, rows, cols, static_cast<TO*>(out))
+  if (q_dtype == B200MOE_FP8_E4M3) {
+    if (out_dtype == B200MOE_BF16) DQS(__nv_bfloat16, float, true); else DQS(__half, float, true);
+  } else {
+    if (out_dtype == B200MOE_BF16) DQS(__nv_bfloat16, __half, false); else DQS(__half, __half, false);
+  }
+#undef DQS
+  return check_launch("dequant_sum");
+}
 
 extern "C" int b200moe_act_quant_fp8(const void* x, int x_dtype, int64_t rows, int64_t cols,
                                      void* y, int64_t y_row_stride_bytes, float* s,

@@ -4,6 +4,9 @@
 
 #include <cuda.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace b200moe {
@@ -39,6 +42,40 @@ inline int make_tensor_map_u8(CUtensorMap* m, const void* base, uint64_t rows, u
                          box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200MOE_BAD_ARG, "cuTensorMapEncodeTiled failed with %d", (int)r);
+  return B200MOE_OK;
+}
+
+// Encoding a tensor map costs a few microseconds of host time and depends on nothing but its arguments, so the
+// encoded maps are kept: the key is (base, rows, cols, row stride, box rows).  A layer's weights and workspaces
+// keep their addresses from step to step, so every launch after the first finds its maps here.  The table is
+// process-wide, mutex-protected, and simply cleared when it reaches 1024 entries.
+struct TensorMapKey {
+  const void* base; uint64_t rows, cols, stride; uint32_t box;
+  bool operator==(const TensorMapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && stride == o.stride && box == o.box;
+  }
+};
+struct TensorMapKeyHash {
+  size_t operator()(const TensorMapKey& k) const {
+    uint64_t h = reinterpret_cast<uintptr_t>(k.base);
+    for (uint64_t v : {k.rows, k.cols, k.stride, static_cast<uint64_t>(k.box)}) h = (h ^ v) * 0x9E3779B97F4A7C15ull + (h >> 29);
+    return static_cast<size_t>(h);
+  }
+};
+inline int cached_tensor_map_u8(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
+                                uint64_t row_stride, uint32_t box_rows) {
+  static std::mutex mu;
+  static std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> table;
+  const TensorMapKey key{base, rows, cols, row_stride, box_rows};
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    auto it = table.find(key);
+    if (it != table.end()) { *m = it->second; return B200MOE_OK; }
+  }
+  if (int rc = make_tensor_map_u8(m, base, rows, cols, row_stride, box_rows)) return rc;
+  std::lock_guard<std::mutex> lock(mu);
+  if (table.size() >= 1024) table.clear();
+  table.emplace(key, *m);
   return B200MOE_OK;
 }
 

@@ -220,6 +220,10 @@ class DeepseekV3MoE(nn.Module):
         assert self.strategy in ("all2all", "allreduce")
         # default ("auto"): "fused" for fp8_block, "nccl" for the int4 methods
         self.exchange = getattr(config, "ep_exchange", "auto") if self.ep_size > 1 else "none"
+        # payload of the all-reduce of the "allreduce" strategy: None = bf16 NCCL all-reduce; "fp8" / "int8" = the
+        # reference's quantized all-reduce (quant_communication/quant_all2all_allreduce.py:52-99)
+        self.allreduce_quant = getattr(config, "allreduce_quant", None)
+        assert self.allreduce_quant in (None, "fp8", "int8")
         if self.strategy == "allreduce":
             self.exchange, self.passes = "none", 1
         if self.exchange == "auto":
@@ -231,9 +235,9 @@ class DeepseekV3MoE(nn.Module):
         self._fx = None
         self.recv_capacity = float(getattr(config, "ep_recv_capacity", 2.0))   # receive rows / (T*k)
         self._xch = None
-        if self.passes > 1:
-            # leave SMs for the NCCL kernels that run beside the expert GEMMs (config.ep_gemm_ctas)
-            N.check(N.lib().b200moe_set_gemm_max_ctas(int(getattr(config, "ep_gemm_ctas", 0))))
+        # with pipeline passes the expert GEMMs leave SMs for the NCCL kernels that run beside them
+        # (config.ep_gemm_ctas; passed with each of this layer's GEMM calls)
+        self._gemm_ctas = int(getattr(config, "ep_gemm_ctas", 0)) if self.passes > 1 else 0
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         self._dev = dev
         reg = lambda name, t: self.register_buffer(name, t, persistent=True)
@@ -457,7 +461,7 @@ class DeepseekV3MoE(nn.Module):
                                               BLOCK_SIZE=512)
         self._mark("permute_quant")
         ctx = {}
-        run = getattr(self, "_experts_" + self.method)
+        run = self._experts
 
         if ep == 1:
             self.last_recv_rows = S
@@ -553,9 +557,19 @@ class DeepseekV3MoE(nn.Module):
         out = torch.empty((T, H), dtype=x.dtype, device=x.device)
         G.post_reorder_triton_kernel[(T,)](down, out, src2dst, ids, topk_weight, lo, hi, k, H, BLOCK_SIZE=512)
         self._mark("post_reorder")
-        dist.all_reduce(out, op=dist.ReduceOp.SUM)
+        if self.allreduce_quant is None:
+            dist.all_reduce(out, op=dist.ReduceOp.SUM)
+        else:
+            ep_comm.quant_allreduce(out, self._ar_quant, G.dequant_sum)
         self._mark("all_reduce")
         return out
+
+    def _ar_quant(self, t):
+        """Quantizer of the all-reduce payload: e4m3 with f32 1x128 scales, or int8 (floor(v + 0.5), the rounding
+        of the reference's communication quantizer, quant_communication/quant_utils.py:27-28) with f16 scales."""
+        if self.allreduce_quant == "fp8":
+            return fp8_kernel.act_quant(t)
+        return w4a8_kernel.act_quant(t)
 
     def share_exchange_buffers(self, other: "DeepseekV3MoE"):
         """Uses `other`'s peer-mapped receive/return buffers (ep_exchange="fused") instead of allocating
@@ -664,6 +678,13 @@ class DeepseekV3MoE(nn.Module):
         return self._cs
 
     # ---- expert FFNs over the permuted rows ---------------------------------------------
+    def _experts(self, *args):
+        fn = getattr(self, "_experts_" + self.method)
+        if self._gemm_ctas:
+            with G.gemm_options(max_ctas=self._gemm_ctas):
+                return fn(*args)
+        return fn(*args)
+
     def _experts_fp8_block(self, ctx, buf, rows, seg, widx, down, rng):
         H, I = self.config.hidden_size, self.config.moe_intermediate_size
         a_q, a_s = buf[:, :H], buf[:, H:H + (H // 128) * 4].view(torch.float32)

@@ -332,3 +332,46 @@ class FusedExchange:
         rank has reached it on its stream, i.e. after the kernels that stored into this rank's buffers
         (which end with a system-scope fence) have finished."""
         dist.all_reduce(self._flag, group=self.group)
+
+
+# --------------------------------------------------------------------------------------------
+# Quantized all-reduce of the all-gather/all-reduce strategy's output (the scheme of the reference's
+# quant_communication/quant_all2all_allreduce.py:52-99): reduce-scatter as an all-to-all of quantized
+# chunks, local dequantize + f32 sum, re-quantize, all-gather, dequantize.  The payload travels as a
+# uint8 view ("NCCL does not support FP8 directly", :38) and the scales as a second message (:69-70).
+# --------------------------------------------------------------------------------------------
+def quant_allreduce(x: torch.Tensor, quant, dequant_sum, group=None) -> torch.Tensor:
+    """In-place sum of x [T, H] over the ranks of `group` through 8-bit payloads.
+
+    quant(t [R, H]) -> (payload uint8-viewable [R, H], scales [R, H/128]);
+    dequant_sum(payload [n, R, H], scales [n, R, H/128], out [R, H]) writes, in out's dtype, the sum over the
+    n sources of the dequantized chunks (each rounded to out's dtype first, f32 accumulation).
+    Rows are padded to a multiple of the group size; rank r reduces rows [r*R, (r+1)*R)."""
+    ep = dist.get_world_size(group)
+    rank = dist.get_rank(group)
+    T, H = x.shape
+    R = -(-T // ep)                                   # rows per rank chunk
+    if R * ep != T:
+        xp = x.new_zeros(R * ep, H)
+        xp[:T].copy_(x)
+    else:
+        xp = x
+    # ---- stage A: quantize all chunks, exchange, dequantize + sum my chunk
+    q, s = quant(xp)
+    q8 = q.view(torch.uint8).view(ep, R, H)
+    s3 = s.view(ep, R, -1)
+    rq, rs = torch.empty_like(q8), torch.empty_like(s3)
+    dist.all_to_all_single(rq, q8.contiguous(), group=group)
+    dist.all_to_all_single(rs, s3.contiguous(), group=group)
+    mine = x.new_empty(R, H)
+    dequant_sum(rq.view(q.dtype), rs, mine)
+    # ---- stage B: quantize the reduced chunk, gather everyone's, dequantize
+    q2, s2 = quant(mine)
+    gq = torch.empty(ep * R, H, dtype=torch.uint8, device=x.device)
+    gs = torch.empty(ep * R, s2.shape[-1], dtype=s2.dtype, device=x.device)
+    dist.all_gather_into_tensor(gq, q2.view(torch.uint8).view(R, H).contiguous(), group=group)
+    dist.all_gather_into_tensor(gs, s2.view(R, -1).contiguous(), group=group)
+    full = x.new_empty(ep * R, H)
+    dequant_sum(gq.view(q.dtype).view(1, ep * R, H), gs.view(1, ep * R, -1), full)
+    x.copy_(full[:T])
+    return x

@@ -6,6 +6,9 @@ The reference launches its Triton kernels as ``kernel[(grid,)](args, BLOCK_SIZE=
 exported here accept the same syntax; the grid and BLOCK_SIZE are ignored because
 the CUDA launchers size themselves.
 """
+import contextlib
+import ctypes as C
+import threading
 from typing import List, Optional
 
 import torch
@@ -13,6 +16,24 @@ import torch
 from .. import _native as N
 
 _workspaces = {}
+_tls = threading.local()
+
+
+@contextlib.contextmanager
+def gemm_options(max_ctas: int = 0, pair_mode: int = 0):
+    """Launch options for the grouped GEMMs called inside the `with` block by this thread (b200moe_gemm_opts:
+    grid cap, CTA pairs).  They are passed with every call; the library keeps no such state."""
+    prev = getattr(_tls, "opts", None)
+    _tls.opts = N.GemmOpts(int(max_ctas), int(pair_mode))
+    try:
+        yield
+    finally:
+        _tls.opts = prev
+
+
+def _opts():
+    o = getattr(_tls, "opts", None)
+    return None if o is None else C.byref(o)
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
@@ -171,7 +192,7 @@ def grouped_gemm_fp8(a, a_s, b, b_s, seg_indptr, weight_indices, c, c_s=None, ep
         N.ptr(c), c_dtype, c.stride(0) * c.element_size(),
         N.ptr(c_s), 0 if c_s is None else c_s.stride(0), M, Nn, K, G, W,
         N.ptr(seg_indptr), N.ptr(weight_indices), epilogue, N.ptr(c_row_map), N.ptr(c_row_addr),
-        N.ptr(status_word), N.stream()))
+        N.ptr(status_word), _opts(), N.stream()))
     return c
 
 
@@ -223,7 +244,7 @@ def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=N
     N.check(N.lib().b200moe_grouped_gemm_i8(
         N.ptr(a), a.stride(0), N.ptr(a_s), a_s.stride(0), N.ptr(b), N.ptr(b_s), N.ptr(c), N.dtype_code(c.dtype),
         c.stride(0) * c.element_size(), M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr),
-        N.ptr(weight_indices), N.ptr(status_word), N.stream()))
+        N.ptr(weight_indices), N.ptr(status_word), _opts(), N.stream()))
     return c
 
 
@@ -243,12 +264,12 @@ def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, st
         N.check(N.lib().b200moe_grouped_gemm_f16(
             N.ptr(a), a.stride(0) * 2, N.ptr(b), N.ptr(c), N.dtype_code(c.dtype), c.stride(0) * c.element_size(),
             M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices),
-            N.ptr(status_word), N.stream()))
+            N.ptr(status_word), _opts(), N.stream()))
         return c
     N.check(N.lib().b200moe_grouped_gemm_bf16(
         N.ptr(a), a.stride(0) * 2, N.ptr(b), N.ptr(c), N.dtype_code(c.dtype), c.stride(0) * c.element_size(),
         M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices), epilogue,
-        N.ptr(status_word), N.stream()))
+        N.ptr(status_word), _opts(), N.stream()))
     return c
 
 
@@ -282,3 +303,18 @@ def grouped_gemm_triton(a: torch.Tensor, b: torch.Tensor, c: torch.Tensor, batch
     grouped_gemm_fp8(a, scale_a, b, _f32_or_none(scale_b).contiguous(), seg[: batch_size + 1],
                      weight_indices, c, epilogue=0)
     return c
+
+
+def dequant_sum(payload: torch.Tensor, scales: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out [R, H] = sum over sources of dequantized chunks (each rounded to out's dtype, f32 accumulation).
+    payload [n, R, H] e4m3 (f32 scales [n, R, H/128]) or int8 (f16 scales); the middle and last steps of the
+    quantized all-reduce (reference quant_communication/quant_all2all_allreduce.py:73-80, 96-99)."""
+    N.require_cuda(payload, scales, out)
+    assert payload.is_contiguous() and scales.is_contiguous() and out.is_contiguous()
+    n, R, H = payload.shape
+    assert tuple(scales.shape) == (n, R, H // 128) and tuple(out.shape) == (R, H)
+    qd = N.FP8_E4M3 if payload.dtype == torch.float8_e4m3fn else N.dtype_code(payload.dtype)
+    N.check(N.lib().b200moe_dequant_sum(N.ptr(payload), qd, H, R * H, N.ptr(scales), N.dtype_code(scales.dtype),
+                                        H // 128, R * (H // 128), n, R, H, N.ptr(out), N.dtype_code(out.dtype),
+                                        N.stream()))
+    return out

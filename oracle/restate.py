@@ -290,6 +290,47 @@ def weight_dequant_int8(x: torch.Tensor, s: torch.Tensor, block_size: int = 128,
 
 
 # --------------------------------------------------------------------------
+# Quantized all-reduce  (quant_communication/quant_all2all_allreduce.py:52-99)
+# --------------------------------------------------------------------------
+def comm_quant(x: torch.Tensor, kind: str):
+    """Payload quantizer of the quantized all-reduce over 1x128 groups: kind "fp8" = act_quant_fp8
+    (e4m3, f32 scales); kind "int8" = quant_communication/quant_utils.py:9-32 (s = amax/127 stored as f16,
+    y = floor(x/s + 0.5)), which is act_quant_int8 with rounding='floor_half'."""
+    return act_quant_fp8(x) if kind == "fp8" else act_quant_int8(x, rounding="floor_half")
+
+
+def comm_dequant_sum(q: torch.Tensor, s: torch.Tensor, out_dtype):
+    """quant_all2all_allreduce.py:73-80: q [n, R, H], s [n, R, H/128]; each source is dequantized as
+    quant_utils.py:75-83 / 176-180 do (product in the scales' dtype, cast to the output dtype), the sources
+    are summed in f32 and the sum is cast to the output dtype.  Groups with scale 0 decode to zero."""
+    se = s.repeat_interleave(128, dim=-1)
+    v = torch.where(se == 0, torch.zeros((), dtype=torch.float32), q.float())
+    prod = (v * se.float()).to(s.dtype).to(out_dtype)
+    return prod.float().sum(dim=0).to(out_dtype)
+
+
+def quant_allreduce(xs, kind: str):
+    """The whole scheme for a list of per-rank tensors [T, H] (ranks simulated in-process): returns the tensor
+    every rank ends up with.  Rows are padded to a multiple of the rank count."""
+    ep = len(xs)
+    T, H = xs[0].shape
+    R = -(-T // ep)
+    dt = xs[0].dtype
+    pad = [torch.cat([x, x.new_zeros(R * ep - T, H)]) for x in xs]
+    qs = [comm_quant(p, kind) for p in pad]
+    chunks = []
+    for r in range(ep):                                   # rank r reduces rows [r*R, (r+1)*R)
+        q = torch.stack([qs[s_][0][r * R:(r + 1) * R] for s_ in range(ep)])
+        s = torch.stack([qs[s_][1][r * R:(r + 1) * R] for s_ in range(ep)])
+        chunks.append(comm_dequant_sum(q, s, dt))
+    out = []
+    for c in chunks:
+        q2, s2 = comm_quant(c, kind)
+        out.append(comm_dequant_sum(q2.unsqueeze(0), s2.unsqueeze(0), dt))
+    return torch.cat(out)[:T]
+
+
+# --------------------------------------------------------------------------
 # Reorder / activation / combine kernels  (moe/group_gemm_kernel.py)
 # --------------------------------------------------------------------------
 def pre_reorder(x, src2dst, topk_ids, a1_scales, start_expert_id, end_expert_id,

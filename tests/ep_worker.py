@@ -30,6 +30,7 @@ def main():
     cfg.ep_strategy = strategy
     cfg.ep_passes = int(os.environ.get("EP_PASSES", "1"))
     cfg.ep_exchange = os.environ.get("EP_EXCHANGE", "nccl")
+    cfg.allreduce_quant = os.environ.get("EP_AR_QUANT") or None
     layer = DeepseekV3MoE(cfg, device=dev).eval()
     WL.fill_layer_cpu_seeded(layer, shape)
     x = WL.tokens(shape, rank=rank if strategy == "all2all" else 0)
@@ -62,7 +63,9 @@ def main():
     rows = torch.tensor([layer.last_recv_rows, own], device=dev)
     dist.all_reduce(rows)
     assert int(rows[0]) == int(rows[1]), "rows are not conserved across the exchange"
-    assert err < 1e-2, f"rank {rank}: rel_fro {err}"
+    # an 8-bit all-reduce payload adds its own quantization error twice (int8: ~1e-2, e4m3: a few per cent)
+    tol = {None: 1e-2, "int8": 2e-2, "fp8": 6e-2}[cfg.allreduce_quant]
+    assert err < tol, f"rank {rank}: rel_fro {err}"
     print(f"rank {rank} ok rel_fro={err:.2e} recv_rows={layer.last_recv_rows}", flush=True)
     dist.barrier()
     dist.destroy_process_group()

@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol(native):
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} declared in b200moe.h but not exported"
     assert declared == set(native.SIGNATURES), "ctypes table and header disagree"
-    assert lib.b200moe_abi_version() == 1
+    assert lib.b200moe_abi_version() == 2
     assert lib.b200moe_status_string(0) == b"ok"
 
 
@@ -225,3 +225,53 @@ def test_sglang_mirror_exports_grouped_gemm_runner():
         z = torch.zeros(2, 128, dtype=torch.float16)
         r(z, torch.zeros(1, 128, 128, dtype=torch.float16), torch.zeros(2, 128, dtype=torch.float16), 1, True,
           torch.tensor([0, 2]))
+
+
+_QAR_WORKER = r'''
+import os, sys, torch, torch.distributed as dist
+sys.path.insert(0, sys.argv[1])
+from llm_kernels_b200.moe import ep_comm
+from oracle import restate as R
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+dist.init_process_group("gloo", rank=rank, world_size=world)
+T, H = 37, 256                                   # 37 rows: not a multiple of the rank count -> padded chunk
+xs = []
+for r in range(world):                           # every rank can rebuild every rank's input (seeded)
+    g = torch.Generator().manual_seed(500 + r)
+    t = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    t[3 + r] = 0                                 # an all-zero row: zero scale, NaN payload, must decode to zero
+    xs.append(t)
+for kind in ("int8", "fp8"):
+    x = xs[rank].clone()
+    quant = lambda t: R.comm_quant(t, kind)
+    def dsum(q, s, out):
+        out.copy_(R.comm_dequant_sum(q, s, out.dtype))
+    ep_comm.quant_allreduce(x, quant, dsum)
+    want = R.quant_allreduce(xs, kind)           # the scheme with the ranks simulated in one process
+    assert torch.equal(x, want), kind
+    exact = sum(t.float() for t in xs)
+    if kind == "int8":                           # the reference's own acceptance test (quant_all2all_allreduce.py:104)
+        assert torch.allclose(x.float(), exact, rtol=1e-2, atol=1e-1)
+    else:                                        # e4m3 keeps 3 mantissa bits, twice: a few per cent
+        assert R.rel_fro(x.float(), exact) < 6e-2
+    assert not bool(x.isnan().any())
+dist.destroy_process_group()
+print("OK", rank)
+'''
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_quantized_allreduce_plumbing_gloo(tmp_path, world):
+    """ep_comm.quant_allreduce (all-to-all of quantized chunks, local sum, re-quantize, all-gather) on gloo ranks
+    with the oracle's quantizers plugged in: identical to the oracle's in-process simulation of the scheme."""
+    script = tmp_path / "qar_worker.py"
+    script.write_text(_QAR_WORKER)
+    port = 29500 + (os.getpid() + 17 * world) % 1000
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        procs.append(subprocess.Popen([sys.executable, str(script), ROOT], env=env, stdout=subprocess.PIPE,
+                                      stderr=subprocess.STDOUT, text=True))
+    for p in procs:
+        out, _ = p.communicate(timeout=180)
+        assert p.returncode == 0, out

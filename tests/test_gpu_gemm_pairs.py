@@ -19,17 +19,14 @@ def dev():
 
 @pytest.fixture
 def modes(dev):
-    import llm_kernels_b200._native as N
+    from llm_kernels_b200.moe import group_gemm_kernel as G
 
     def run(fn):
         outs = []
         for mode in (0, 1):
-            N.check(N.lib().b200moe_set_gemm_pair_mode(mode))
-            try:
+            with G.gemm_options(pair_mode=mode):
                 outs.append(fn())
                 torch.cuda.synchronize()
-            finally:
-                N.check(N.lib().b200moe_set_gemm_pair_mode(0))
         return outs
     return run
 

@@ -440,6 +440,47 @@ def test_grouped_gemm_fp8_swiglu_epilogue(dev, counts, I, K, W, act):
     assert float((hq.cpu() != ho.view(torch.uint8)).float().mean()) < 0.01
 
 
+@pytest.mark.parametrize("kind", ["fp8", "int8"])
+def test_quantized_allreduce_kernels_emulated_ranks(dev, kind):
+    """The device pieces of the quantized all-reduce (reference quant_communication/quant_all2all_allreduce.py:52-99)
+    with 4 ranks emulated on one GPU: quantize every rank's tensor, dequantize + sum each rank's chunk
+    (b200moe_dequant_sum), re-quantize, dequantize.  Bit-exact against the oracle's simulation of the scheme,
+    all-zero rows included; the int8 result also passes the reference's own allclose(rtol 1e-2, atol 1e-1)."""
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    from llm_kernels_b200.quantization import fp8_kernel, w4a8_kernel
+    ep, T, H = 4, 40, 512
+    g = torch.Generator().manual_seed(77)
+    xs = [torch.randn(T, H, generator=g).to(torch.bfloat16) for _ in range(ep)]
+    xs[2][5] = 0
+    xs[0][17, 128:256] = 0
+    quant = fp8_kernel.act_quant if kind == "fp8" else w4a8_kernel.act_quant
+    R_ = T // ep
+    qs = [quant(x.to(dev)) for x in xs]
+    for (q, s_), x in zip(qs, xs):                       # the quantizers themselves against the oracle
+        qo, so = R.comm_quant(x, kind)
+        assert torch.equal(s_.cpu(), so)
+        live = so.repeat_interleave(128, dim=-1) != 0        # all-zero groups: 0/0 payload, decoded as zero anyway
+        assert torch.equal(q.cpu().view(torch.uint8)[live], qo.view(torch.uint8)[live])
+    chunks = []
+    for r in range(ep):
+        q = torch.stack([qs[s_][0][r * R_:(r + 1) * R_] for s_ in range(ep)])
+        sc = torch.stack([qs[s_][1][r * R_:(r + 1) * R_] for s_ in range(ep)])
+        out = torch.empty(R_, H, dtype=torch.bfloat16, device=dev)
+        G.dequant_sum(q.contiguous(), sc.contiguous(), out)
+        q2, s2 = quant(out)
+        fin = torch.empty(R_, H, dtype=torch.bfloat16, device=dev)
+        G.dequant_sum(q2.unsqueeze(0), s2.unsqueeze(0), fin)
+        chunks.append(fin)
+    got = torch.cat(chunks).cpu()
+    want = R.quant_allreduce(xs, kind)
+    assert torch.equal(got, want)
+    exact = sum(x.float() for x in xs)
+    if kind == "int8":
+        assert torch.allclose(got.float(), exact, rtol=1e-2, atol=1e-1)
+    else:
+        assert R.rel_fro(got.float(), exact) < 6e-2
+
+
 # ---------------------------------------------------------------- int4 weight paths
 def test_w4a8_weight_quant_expand_and_gemm_match_reference_vectors(dev, golden):
     from llm_kernels_b200.quantization import w4a8_kernel

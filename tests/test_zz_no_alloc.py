@@ -48,6 +48,10 @@ def test_noalloc_matches_workspace_entry_point_twice():
         for a, b in zip(want, got):
             assert torch.equal(a, b)            # integer results: bit-exact
         assert int(got[2][-1]) == T * k
+        # and both against the CPU oracle's stable sort (reference moe/group_gemm_kernel.py:48-78)
+        from oracle import restate as R
+        for a, b in zip(R.run_moe_ep_preproess(ids.cpu().view(T, k), E), got):
+            assert torch.equal(a, b.cpu())
 
 
 def test_noalloc_rejects_oversized_problem_and_handles_empty():
