@@ -326,8 +326,17 @@ def other_configs(dev, peaks, fp8_peak):
             layer(x)
         layer.check_status()
         ms = _time_launches(lambda i: layer(x), 10, dev)
+        layer.stage_events = []
+        for _ in range(5):
+            layer(x)
+        torch.cuda.synchronize(dev)
+        ev, st = layer.stage_events, {}
+        layer.stage_events = None
+        for (n0, e0), (n1, e1) in zip(ev[:-1], ev[1:]):
+            if n1 != "start":
+                st[n1] = st.get(n1, 0.0) + e0.elapsed_time(e1) / 5
         rows = shape.tokens * shape.top_k
-        rec = {"ms_per_step": ms, "tokens_per_s": shape.tokens / (ms * 1e-3),
+        rec = {"ms_per_step": ms, "tokens_per_s": shape.tokens / (ms * 1e-3), "stages_ms": st,
                "gemm_tflops_whole_step": 6.0 * shape.hidden * shape.inter * rows / (ms * 1e-3) / 1e12}
         wbytes = shape.experts * 3 * shape.hidden * shape.inter // 2          # packed int4
         rec["packed_weight_gbs_whole_step"] = wbytes / (ms * 1e-3) / 1e9

@@ -352,6 +352,45 @@ B200MOE_API int b200moe_grouped_gemm_i8(const void* a, int64_t a_row_stride_byte
                             const int64_t* seg_indptr, const int64_t* weight_indices,
                             int32_t* status_word, const b200moe_gemm_opts* opts, void* stream);
 
+/* Grouped w4a8 GEMM with the int4 -> int8 step inside the kernel: w4a8_gemm (quantization/w4a8_kernel.py:317-448,
+ * unpack and (q - z4) * s4 in its K loop at :362-380), grouped as grouped_gemm_triton
+ * (moe/group_gemm_kernel.py:291-513).  The packed weights go from HBM to shared memory as they are (0.5 byte per
+ * weight); converter warps split the words into nibbles with byte permutes, apply (q - z4) * s4 four values at a time
+ * and write the int8 operand tile the tensor core reads.  Results are bit-identical to b200moe_w4a8_expand_int8
+ * followed by b200moe_grouped_gemm_i8.  Each weight tile is converted once per m-tile, so this is the entry point
+ * for few rows per group (decode); with many rows per expert, expand once and use b200moe_grouped_gemm_i8.
+ *   a int8 [M_total, K], a_s f32 [M_total, K/128] (row strides given); b_packed int32 [num_weights, N/8, K]
+ *   (pack_weights_over_rows, quantization/bitpack.py:9-36); s4z4_t int8 [num_weights, K/128, N, 2]: the pairs
+ *   (s4[n,kb], z4[n,kb]) of quantization/w4a8_kernel.py:228-262, transposed so that one K block's pairs are
+ *   contiguous; b_s f32 [num_weights, N/128, K/128].
+ *   epilogue 0: c [M_total, N] f32/f16/bf16.  epilogue 1 / 4: SiLU(gate)*up / GELU(gate)*up with the roundings of the
+ *   unfused chain (moe/group_gemm_kernel.py:120-235), then act_quant of quantization/w4a8_kernel.py:145-193
+ *   (s = amax/127, y = floor(h/s + 0.5)): c int8 [M_total, N/2], c_s f32 [M_total, N/256] holding the f16-rounded
+ *   scales.  K % 128 == 0, N % 128 == 0 (fused epilogues: N % 256 == 0). */
+B200MOE_API int b200moe_grouped_gemm_w4a8(const void* a, int64_t a_row_stride_bytes, const float* a_s,
+                              int64_t a_s_row_stride, const void* b_packed, const void* s4z4_t,
+                              const float* b_s, void* c, int c_dtype, int64_t c_row_stride_bytes,
+                              float* c_s, int64_t c_s_row_stride, int64_t M_total, int64_t N, int64_t K,
+                              int num_groups, int num_weights, const int64_t* seg_indptr,
+                              const int64_t* weight_indices, int epilogue, int32_t* status_word,
+                              void* stream);
+
+/* Grouped w4a16 GEMM (asymmetric group-128 int4 weights, bf16 activations) with the dequantization inside the kernel:
+ * the counterpart, for few rows per group, of the reference's w4a16 kernel that dequantizes in registers
+ * (fast_dequant/simple_marlin/marlin_w4a16_gemm.cu:44-64, 86-280), here with a zero-point and bf16.  Packed words travel
+ * from HBM as they are; converter warps turn each word into eight bf16 values (q - zero) * scale (0x4300 | q is the bf16
+ * number 128 + q; two exact subtractions, one rounded product) and write the operand tile the tensor core reads; the
+ * K loop accumulates in TMEM.  Bit-identical to b200moe_w4a16_expand_bf16 followed by b200moe_grouped_gemm_bf16.
+ *   a bf16 [M_total, K]; b_packed int32 [num_weights, N, K/8] (pack_weights_over_cols, quantization/bitpack.py:38-67);
+ *   scale_zero_t bf16 [num_weights, K/128, N, 2]: (scale, zero) pairs with one K group's pairs contiguous.
+ *   epilogue 0: c [M_total, N] f32/f16/bf16; 2 / 5: SiLU(gate)*up / GELU(gate)*up, c bf16 [M_total, N/2].
+ *   K % 128 == 0, N % 128 == 0 (fused epilogues: N % 256 == 0). */
+B200MOE_API int b200moe_grouped_gemm_w4a16(const void* a, int64_t a_row_stride_bytes, const void* b_packed,
+                               const void* scale_zero_t, void* c, int c_dtype, int64_t c_row_stride_bytes,
+                               int64_t M_total, int64_t N, int64_t K, int num_groups, int num_weights,
+                               const int64_t* seg_indptr, const int64_t* weight_indices, int epilogue,
+                               int32_t* status_word, void* stream);
+
 /* Grouped bf16 x bf16 GEMM with f32 accumulation in TMEM (the unquantized branch of
  * grouped_gemm_triton, moe/group_gemm_kernel.py:410-412; used by the w4a16 path after
  * b200moe_w4a16_expand_bf16).  a bf16 [M_total, K] (row stride in bytes), b bf16

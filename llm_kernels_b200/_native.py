@@ -56,6 +56,9 @@ SIGNATURES = {
     "b200moe_w4a16_expand_bf16": (_i, [_p, _p, _p, _p, _i64, _i64, _p]),
     "b200moe_grouped_gemm_i8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i,
                                      _p, _p, _p, _p, _p]),
+    "b200moe_grouped_gemm_w4a8": (_i, [_p, _i64, _p, _i64, _p, _p, _p, _p, _i, _i64, _p, _i64, _i64, _i64, _i64,
+                                       _i, _i, _p, _p, _i, _p, _p]),
+    "b200moe_grouped_gemm_w4a16": (_i, [_p, _i64, _p, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p]),
     "b200moe_grouped_gemm_bf16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _i, _p, _p, _p]),
     "b200moe_grouped_gemm_f16": (_i, [_p, _i64, _p, _p, _i, _i64, _i64, _i64, _i64, _i, _i, _p, _p, _p, _p, _p]),
     "b200moe_marlin_expand_f16": (_i, [_p, _p, _p, _i64, _i64, _i64, _p]),

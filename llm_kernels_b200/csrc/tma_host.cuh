@@ -79,6 +79,23 @@ inline int cached_tensor_map_u8(CUtensorMap* m, const void* base, uint64_t rows,
   return B200MOE_OK;
 }
 
+// int32 matrix rows x cols (row stride in bytes); box = box_rows x box_cols words, no swizzle: the tile lands in
+// shared memory as plain [box_rows][box_cols] words.
+inline int make_tensor_map_i32_plain(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
+                                     uint64_t row_stride, uint32_t box_cols, uint32_t box_rows) {
+  EncodeFn enc = get_tensor_map_encoder();
+  if (!enc) return fail(B200MOE_UNSUPPORTED_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {row_stride};
+  const cuuint32_t box[2] = {box_cols, box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(B200MOE_BAD_ARG, "cuTensorMapEncodeTiled (int32) failed with %d", (int)r);
+  return B200MOE_OK;
+}
+
 inline int require_sm100(int* sms) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return fail(B200MOE_UNSUPPORTED_DEVICE, "no CUDA device");

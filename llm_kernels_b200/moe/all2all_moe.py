@@ -274,6 +274,9 @@ class DeepseekV3MoE(nn.Module):
             reg("shared_w13", z(1, 2 * Is, H, dtype=torch.bfloat16))     # [gate_proj ; up_proj]
             reg("shared_w2", z(1, H, Is, dtype=torch.bfloat16))          # down_proj
             self._shared_stream = None
+        # int4 methods: up to this many rows per expert group on average the dequantization runs inside the GEMMs
+        # (every tile converts its weights once); above it the weights are expanded once per forward instead
+        self.w4_fused_rows_per_group = int(getattr(config, "w4_fused_rows_per_group", 96))
         self._buffers_cache = {}
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._last_recv_rows = None
@@ -380,9 +383,9 @@ class DeepseekV3MoE(nn.Module):
         returns `run(x) -> y` (single-rank layers).  The layer's launch sequence is fixed and reads nothing
         back to the host.  For small batches, where the step is a dozen launches of a few microseconds
         each, replaying the graph removes the per-launch host cost.  `y` is a static buffer that the next
-        `run` overwrites; a device-side timeout still shows up in `check_status()`.  With expert
-        parallelism the step contains NCCL collectives; capturing those together with the peer-mapped
-        buffers did not complete on a 2-GPU trial (the ranks blocked in capture), so it is refused."""
+        `run` overwrites; a device-side timeout still shows up in `check_status()`.  Restricted to
+        ep_size == 1: an expert-parallel step interleaves NCCL collectives with kernels that store into
+        peer-mapped buffers, and capturing that sequence is not supported here."""
         assert self.ep_size == 1, "make_graphed supports ep_size == 1"
         cur = torch.cuda.current_stream()
         side = torch.cuda.Stream(device=self._dev)
@@ -701,7 +704,18 @@ class DeepseekV3MoE(nn.Module):
     def _experts_w4a16(self, ctx, buf, rows, seg, widx, down, rng):
         I = self.config.moe_intermediate_size
         a = buf.view(torch.bfloat16)
-        if "w13" not in ctx:      # int4 -> bf16 once per forward, shared by the pipeline passes
+        r0, r1 = rng
+        if (r1 - r0) <= self.w4_fused_rows_per_group * (seg.numel() - 1):
+            # few rows per expert (decode): the packed weights are dequantized inside the GEMMs, once per tile
+            h = self._buf("h_bf16", (rows, I), torch.bfloat16)
+            G.grouped_gemm_w4a16(a, self.w13_qweight, self._pairs("w13", "_scale", "_zero"), seg, widx, h,
+                                 epilogue=5 if self._gelu else 2, status_word=self._status)
+            self._mark("gemm1_swiglu")
+            G.grouped_gemm_w4a16(h, self.w2_qweight, self._pairs("w2", "_scale", "_zero"), seg, widx, down,
+                                 epilogue=0, status_word=self._status)
+            self._mark("gemm2")
+            return
+        if "w13" not in ctx:      # many rows per expert: int4 -> bf16 once per forward, shared by the pipeline passes
             ctx["w13"] = w4a16_kernel.expand_bf16(self.w13_qweight, self.w13_scale, self.w13_zero)
             ctx["w2"] = w4a16_kernel.expand_bf16(self.w2_qweight, self.w2_scale, self.w2_zero)
             self._mark("expand_weights")
@@ -711,22 +725,44 @@ class DeepseekV3MoE(nn.Module):
         G.grouped_gemm_bf16(h, ctx["w2"], seg, widx, down, epilogue=0, status_word=self._status)
         self._mark("gemm2")
 
+    def _pairs(self, name, first="_s4", second="_z4"):
+        """(s4, z4) -- or (scale, zero) -- of a weight in the layout the fused-dequantization kernels read; rebuilt
+        when the tensors change."""
+        s4, z4 = getattr(self, name + first), getattr(self, name + second)
+        key = (s4.data_ptr(), s4._version, z4.data_ptr(), z4._version)
+        hit = self._buffers_cache.get(("pairs", name))
+        if hit is None or hit[0] != key:
+            hit = (key, G.pair_scales_t(s4, z4))
+            self._buffers_cache[("pairs", name)] = hit
+        return hit[1]
+
     def _experts_w4a8(self, ctx, buf, rows, seg, widx, down, rng):
         H, I = self.config.hidden_size, self.config.moe_intermediate_size
         a_q, a_s = buf[:, :H].view(torch.int8), buf[:, H:H + (H // 128) * 4].view(torch.float32)
-        if "w13" not in ctx:      # int4 -> int8 once per forward, shared by the pipeline passes
+        r0, r1 = rng                                   # the rows this call's groups cover
+        h_q = self._buf("h_i8", (rows, I), torch.int8)
+        h_s = self._buf("h_i8_s", (rows, I // 128), torch.float32)
+        groups = seg.numel() - 1
+        if (r1 - r0) <= self.w4_fused_rows_per_group * groups:
+            # few rows per expert (decode): the packed weights are converted inside the GEMMs, once per tile;
+            # act(gate)*up and the int8 re-quantization are GEMM-1's epilogue
+            G.grouped_gemm_w4a8(a_q, a_s, self.w13_qweight, self._pairs("w13"), self.w13_weight_scale, seg, widx,
+                                h_q, h_s, epilogue=4 if self._gelu else 1, status_word=self._status)
+            self._mark("gemm1_swiglu")
+            G.grouped_gemm_w4a8(h_q, h_s, self.w2_qweight, self._pairs("w2"), self.w2_weight_scale, seg, widx,
+                                down, None, epilogue=0, status_word=self._status)
+            self._mark("gemm2")
+            return
+        if "w13" not in ctx:      # many rows per expert: int4 -> int8 once per forward, shared by the pipeline passes
             ctx["w13"] = w4a8_kernel.expand_int8(self.w13_qweight, self.w13_s4, self.w13_z4)
             ctx["w2"] = w4a8_kernel.expand_int8(self.w2_qweight, self.w2_s4, self.w2_z4)
             self._mark("expand_weights")
         gu = self._buf("gateup", (rows, 2 * I), torch.bfloat16)
         G.grouped_gemm_i8(a_q, a_s, ctx["w13"], self.w13_weight_scale, seg, widx, gu, status_word=self._status)
         self._mark("gemm1")
-        r0, r1 = rng                                   # the rows this call's groups cover
         h = self._buf("h_bf16", (rows, I), torch.bfloat16)
         act_mul = G.gelu_and_mul_triton_kernel if self._gelu else G.silu_and_mul_triton_kernel
         act_mul[(r1 - r0,)](gu[r0:r1], h[r0:r1], 2 * I, None, None, 0, 0, BLOCK_SIZE=512)
-        h_q = self._buf("h_i8", (rows, I), torch.int8)
-        h_s = self._buf("h_i8_s", (rows, I // 128), torch.float32)
         q, sc = w4a8_kernel.act_quant(h[r0:r1])
         h_q[r0:r1].copy_(q)
         h_s[r0:r1].copy_(sc)

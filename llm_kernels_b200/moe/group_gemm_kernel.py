@@ -248,6 +248,54 @@ def grouped_gemm_i8(a, a_s, b, b_s, seg_indptr, weight_indices, c, status_word=N
     return c
 
 
+def pair_scales_t(s4: torch.Tensor, z4: torch.Tensor) -> torch.Tensor:
+    """s4, z4 [..., N, K/128] -> [..., K/128, N, 2]: the (s4, z4) int8 pairs (or the (scale, zero) bf16 pairs of the
+    w4a16 format) with one K group's pairs contiguous, the layout the fused-dequantization GEMMs read (built once per
+    weight)."""
+    return torch.stack([s4, z4], dim=-1).transpose(-3, -2).contiguous()
+
+
+def grouped_gemm_w4a8(a, a_s, b_packed, s4z4_t, b_s, seg_indptr, weight_indices, c, c_s=None, epilogue: int = 0,
+                      status_word=None):
+    """tcgen05 grouped w4a8 GEMM with the int4 -> int8 step inside the kernel (reference w4a8_gemm,
+    quantization/w4a8_kernel.py:317-448).  a int8 [M,K] and a_s f32 [M,K/128] (row-strided views allowed),
+    b_packed int32 [W,N/8,K], s4z4_t int8 [W,K/128,N,2] (pair_scales_t), b_s f32 [W,N/128,K/128].
+    epilogue 0: c [M,N]; epilogue 1 / 4: act(gate)*up + int8 re-quantization, c int8 [M,N/2], c_s f32 [M,N/256]."""
+    N.require_cuda(a, a_s, b_packed, s4z4_t, b_s, c)
+    assert a.dtype in (torch.int8, torch.uint8) and b_packed.dtype == torch.int32 and s4z4_t.dtype == torch.int8
+    assert a_s.dtype == torch.float32 and b_s.dtype == torch.float32
+    assert b_packed.is_contiguous() and s4z4_t.is_contiguous() and b_s.is_contiguous()
+    assert a.stride(1) == 1 and a_s.stride(1) == 1
+    M, K = a.shape
+    W, N8, Kb = b_packed.shape
+    Nn = N8 * 8
+    assert Kb == K and tuple(s4z4_t.shape) == (W, K // 128, Nn, 2)
+    c_dtype = N.I8 if epilogue in (1, 4) else N.dtype_code(c.dtype)
+    N.check(N.lib().b200moe_grouped_gemm_w4a8(
+        N.ptr(a), a.stride(0), N.ptr(a_s), a_s.stride(0), N.ptr(b_packed), N.ptr(s4z4_t), N.ptr(b_s),
+        N.ptr(c), c_dtype, c.stride(0) * c.element_size(), N.ptr(c_s), 0 if c_s is None else c_s.stride(0),
+        M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr), N.ptr(weight_indices), epilogue,
+        N.ptr(status_word), N.stream()))
+    return c
+
+
+def grouped_gemm_w4a16(a, b_packed, scale_zero_t, seg_indptr, weight_indices, c, epilogue: int = 0, status_word=None):
+    """tcgen05 grouped w4a16 GEMM with the int4 -> bf16 dequantization inside the kernel.  a bf16 [M,K] (row-strided
+    view allowed), b_packed int32 [W,N,K/8], scale_zero_t bf16 [W,K/128,N,2] (pair_scales_t(scale, zero)).
+    epilogue 0: c [M,N]; 2 / 5: SiLU(gate)*up / GELU(gate)*up, c bf16 [M,N/2]."""
+    N.require_cuda(a, b_packed, scale_zero_t, c)
+    assert a.dtype == torch.bfloat16 and b_packed.dtype == torch.int32 and scale_zero_t.dtype == torch.bfloat16
+    assert b_packed.is_contiguous() and scale_zero_t.is_contiguous() and a.stride(1) == 1
+    M, K = a.shape
+    W, Nn, K8 = b_packed.shape
+    assert K8 * 8 == K and tuple(scale_zero_t.shape) == (W, K // 128, Nn, 2)
+    N.check(N.lib().b200moe_grouped_gemm_w4a16(
+        N.ptr(a), a.stride(0) * 2, N.ptr(b_packed), N.ptr(scale_zero_t), N.ptr(c), N.dtype_code(c.dtype),
+        c.stride(0) * c.element_size(), M, Nn, K, seg_indptr.numel() - 1, W, N.ptr(seg_indptr),
+        N.ptr(weight_indices), epilogue, N.ptr(status_word), N.stream()))
+    return c
+
+
 def grouped_gemm_bf16(a, b, seg_indptr, weight_indices, c, epilogue: int = 0, status_word=None):
     """tcgen05 grouped bf16 or f16 GEMM (reference: the scale-free branch of grouped_gemm_triton,
     :410-412).  epilogue 0: c [M,N]; epilogue 2 / 5 (bf16 operands only): SiLU(gate)*up / GELU(gate)*up fused,

@@ -499,6 +499,74 @@ def test_w4a8_weight_quant_expand_and_gemm_match_reference_vectors(dev, golden):
     assert R.rel_fro(out.cpu(), t(c["c"])) < 1e-6
 
 
+def _w4a8_case(seed, counts, N, K, W, dev):
+    g = torch.Generator().manual_seed(seed)
+    M = sum(counts)
+    w = [torch.randn(N, K, generator=g) * 0.02 for _ in range(W)]
+    qz = [R.w4a8_weight_quant(x) for x in w]                       # (packed, s f16, s4, z4)
+    packed = torch.stack([t_[0] for t_ in qz]).to(dev)
+    b_s = torch.stack([t_[1].float() for t_ in qz]).to(dev)
+    s4 = torch.stack([t_[2] for t_ in qz]).to(dev)
+    z4 = torch.stack([t_[3] for t_ in qz]).to(dev)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    a, a_s = R.act_quant_int8(x, rounding="floor_half")
+    seg = torch.zeros(len(counts) + 1, dtype=torch.int64); seg[1:] = torch.cumsum(torch.tensor(counts), 0)
+    return qz, packed, b_s, s4, z4, a.to(dev), a_s.float().to(dev), seg.to(dev), M
+
+
+@pytest.mark.parametrize("counts,N,K,W,widx", [([5, 0, 65, 27], 256, 256, 4, None), ([300, 129, 1], 384, 1024, 3, [2, 0, 1]),
+                                               ([16] * 12, 512, 2048, 12, None)])
+def test_grouped_gemm_w4a8_fused_dequant_plain(dev, counts, N, K, W, widx):
+    """The GEMM that converts int4 -> int8 inside the kernel must equal, bit for bit, the expansion kernel followed
+    by the int8 grouped GEMM (same int8 operands, same per-K-block f32 promotion), and agree with the oracle's
+    w4a8_gemm (reference quantization/w4a8_kernel.py:317-448)."""
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    from llm_kernels_b200.quantization import w4a8_kernel
+    qz, packed, b_s, s4, z4, a, a_s, seg, M = _w4a8_case(51, counts, N, K, W, dev)
+    wi = None if widx is None else torch.tensor(widx, dtype=torch.int64, device=dev)
+    for dt in (torch.float32, torch.bfloat16):
+        c1 = torch.full((M, N), float("nan"), dtype=dt, device=dev)
+        G.grouped_gemm_w4a8(a, a_s, packed, G.pair_scales_t(s4, z4), b_s, seg, wi, c1)
+        c2 = torch.full((M, N), float("nan"), dtype=dt, device=dev)
+        G.grouped_gemm_i8(a, a_s, w4a8_kernel.expand_int8(packed, s4, z4), b_s, seg, wi, c2)
+        torch.cuda.synchronize()
+        assert torch.equal(c1, c2)
+    segl = seg.tolist()
+    for gi in range(len(counts)):
+        m0, m1 = segl[gi], segl[gi + 1]
+        if m1 > m0:
+            e = gi if widx is None else widx[gi]
+            ref = R.w4a8_gemm(a[m0:m1].cpu(), a_s[m0:m1].cpu().to(torch.float16), *qz[e], out_dtype=torch.float32)
+            assert R.rel_fro(c1[m0:m1].cpu().float(), ref) < 3e-3          # c1 is the bf16 result here
+
+
+@pytest.mark.parametrize("act", ["silu", "gelu"])
+@pytest.mark.parametrize("counts,I,K,W", [([5, 0, 65, 27], 128, 256, 4), ([33] * 8, 256, 1024, 8), ([140, 3], 128, 512, 2)])
+def test_grouped_gemm_w4a8_fused_epilogue(dev, counts, I, K, W, act):
+    """Fused act(gate)*up + int8 re-quantization epilogue: int8 rows and scales identical to the unfused chain
+    (int8 GEMM to bf16, silu/gelu_and_mul, act_quant with floor(v + 0.5))."""
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    from llm_kernels_b200.quantization import w4a8_kernel
+    qz, packed, b_s, s4, z4, a, a_s, seg, M = _w4a8_case(53, counts, 2 * I, K, W, dev)
+    hq = torch.full((M, I), 77, dtype=torch.int8, device=dev)
+    hs = torch.full((M, I // 128), -1.0, dtype=torch.float32, device=dev)
+    G.grouped_gemm_w4a8(a, a_s, packed, G.pair_scales_t(s4, z4), b_s, seg, None, hq, hs,
+                        epilogue=1 if act == "silu" else 4)
+    gu = torch.zeros(M, 2 * I, dtype=torch.bfloat16, device=dev)
+    G.grouped_gemm_i8(a, a_s, w4a8_kernel.expand_int8(packed, s4, z4), b_s, seg, None, gu)
+    h = torch.empty(M, I, dtype=torch.bfloat16, device=dev)
+    (G.silu_and_mul_triton_kernel if act == "silu" else G.gelu_and_mul_triton_kernel)[(M,)](gu, h, 2 * I, None, None, 0, 0)
+    q, sc = w4a8_kernel.act_quant(h)
+    torch.cuda.synchronize()
+    # the standalone activation kernel uses expf and an IEEE division, the fused epilogue the fast intrinsics: a bf16
+    # rounding can flip for a handful of values
+    assert float((hq != q).float().mean()) < 2e-3
+    torch.testing.assert_close(hs, sc.float(), rtol=1e-2, atol=0)
+    got = hq.float() * hs.repeat_interleave(128, 1)
+    want = q.float() * sc.float().repeat_interleave(128, 1)
+    assert R.rel_fro(got.cpu(), want.cpu()) < 5e-3
+
+
 @pytest.mark.parametrize("counts,N,K,W", [([5, 0, 65, 27], 256, 256, 4), ([300, 129], 384, 1024, 2)])
 def test_grouped_gemm_i8(dev, counts, N, K, W):
     from llm_kernels_b200.moe import group_gemm_kernel as G
@@ -535,6 +603,38 @@ def test_w4a16_quant_expand_and_gemm(dev):
     c = w4a16_kernel.w4a16_gemm(a.to(dev), packed, sc, z, out_dtype=torch.float32)
     ref = a.float() @ R.w4a16_dequant(qo, so, zo).float().t()
     # same bf16 operands, f32 accumulation: tolerance of the w4a16 path (3e-3) with a wide margin
+    assert R.rel_fro(c.cpu(), ref) < 1e-5
+
+
+@pytest.mark.parametrize("counts,I,K,W,widx", [([5, 0, 65, 27], 128, 256, 4, None), ([16] * 6, 256, 1024, 6, None),
+                                               ([140, 3, 40], 128, 512, 3, [1, 2, 0])])
+def test_grouped_gemm_w4a16_fused_dequant(dev, counts, I, K, W, widx):
+    """The w4a16 GEMM that dequantizes inside the kernel must equal, bit for bit, the expansion kernel followed by the
+    bf16 grouped GEMM, for the plain epilogue and for SiLU(gate)*up / GELU(gate)*up, and agree with the oracle."""
+    from llm_kernels_b200.moe import group_gemm_kernel as G
+    from llm_kernels_b200.quantization import w4a16_kernel
+    g = torch.Generator().manual_seed(59)
+    M = sum(counts)
+    w = torch.randn(W, 2 * I, K, generator=g) * 0.02
+    qs = [w4a16_kernel.weight_quant(w[i].to(dev)) for i in range(W)]
+    packed = torch.stack([q[0] for q in qs]); sc = torch.stack([q[1] for q in qs]); zp = torch.stack([q[2] for q in qs])
+    pairs = G.pair_scales_t(sc, zp)
+    a = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev)
+    seg = torch.zeros(len(counts) + 1, dtype=torch.int64); seg[1:] = torch.cumsum(torch.tensor(counts), 0)
+    seg = seg.to(dev)
+    wi = None if widx is None else torch.tensor(widx, dtype=torch.int64, device=dev)
+    full = w4a16_kernel.expand_bf16(packed, sc, zp)
+    for epi, cols, dt in ((0, 2 * I, torch.float32), (0, 2 * I, torch.bfloat16), (2, I, torch.bfloat16), (5, I, torch.bfloat16)):
+        c1 = torch.full((M, cols), float("nan"), dtype=dt, device=dev)
+        c2 = torch.full((M, cols), float("nan"), dtype=dt, device=dev)
+        G.grouped_gemm_w4a16(a, packed, pairs, seg, wi, c1, epilogue=epi)
+        G.grouped_gemm_bf16(a, full, seg, wi, c2, epilogue=epi)
+        torch.cuda.synchronize()
+        assert torch.equal(c1, c2), epi
+    ref = R.grouped_gemm_plain(a.cpu(), full.cpu(), seg.cpu(), torch.arange(W) if widx is None else torch.tensor(widx),
+                               out_dtype=torch.float32)
+    c = torch.zeros(M, 2 * I, dtype=torch.float32, device=dev)
+    G.grouped_gemm_w4a16(a, packed, pairs, seg, wi, c)
     assert R.rel_fro(c.cpu(), ref) < 1e-5
 
 
