@@ -15,7 +15,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
-SOURCES = ["api.cu", "quant.cu", "router.cu", "route.cu", "permute.cu", "gemm_fp8.cu", "gemm_w4.cu", "bitpack.cu", "w4.cu", "wquant.cu", "ep_fused.cu"]
+SOURCES = ["api.cu", "quant.cu", "router.cu", "route.cu", "permute.cu", "gemm_fp8.cu", "gemm_w4a8.cu", "gemm_w4a16.cu", "bitpack.cu", "w4.cu", "wquant.cu", "ep_fused.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden", "--expt-relaxed-constexpr",

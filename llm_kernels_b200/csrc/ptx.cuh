@@ -65,22 +65,23 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   return t;
 }
 
-// No legitimate wait in these kernels lasts longer than a few milliseconds; two
-// seconds is far beyond that yet finite, so a lost signal ends the kernel instead
-// of hanging the GPU.
-constexpr uint64_t kWaitLimitNs = 2000000000ull;
+// No legitimate wait in these kernels lasts longer than a few milliseconds; the limit is far beyond that yet
+// finite, so a lost signal ends the kernel instead of hanging the GPU.  It is counted in SM clocks (clock64 is a
+// register read; %globaltimer is a round trip to a chip-wide unit that would sit in every hand-over): 4e9 clocks
+// are two seconds at 2 GHz and at most a few seconds at any clock the part runs at.
+constexpr long long kWaitLimitClocks = 4000000000ll;
 
 // Waits for the phase with the given parity.  `abort_flag` (shared memory) is
 // polled so that one role's timeout releases every other role promptly.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity,
                                           volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  const long long t0 = clock64();
   for (uint32_t spin = 1;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 31u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) break;
+      if (clock64() - t0 > kWaitLimitClocks) break;
     }
   }
   *abort_flag = 1;
@@ -102,6 +103,14 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* m
       ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(m)), "r"(smem_u32(bar)),
         "r"(c0), "r"(c1)
       : "memory");
+}
+
+// Untiled bulk copy global -> shared of `bytes` (a multiple of 16; both addresses 16-byte aligned), completion
+// counted in bytes on `bar`.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(reinterpret_cast<uint64_t>(gsrc)), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
 }
 
 // Pair form: issued by each CTA of a pair for its own shared memory; the bytes are counted on the

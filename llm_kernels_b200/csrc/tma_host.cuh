@@ -79,10 +79,11 @@ inline int cached_tensor_map_u8(CUtensorMap* m, const void* base, uint64_t rows,
   return B200MOE_OK;
 }
 
-// int32 matrix rows x cols (row stride in bytes); box = box_rows x box_cols words, no swizzle: the tile lands in
-// shared memory as plain [box_rows][box_cols] words.
+// int32 matrix rows x cols (row stride in bytes); box = box_rows x box_cols words.  Without swizzle the tile lands
+// in shared memory as plain [box_rows][box_cols] words; with it (box_cols must then be 32 words = 128 bytes) the
+// 16-byte chunks of row r sit at chunk position (c ^ (r % 8)).
 inline int make_tensor_map_i32_plain(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
-                                     uint64_t row_stride, uint32_t box_cols, uint32_t box_rows) {
+                                     uint64_t row_stride, uint32_t box_cols, uint32_t box_rows, bool swizzle128 = false) {
   EncodeFn enc = get_tensor_map_encoder();
   if (!enc) return fail(B200MOE_UNSUPPORTED_DEVICE, "cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {cols, rows};
@@ -90,8 +91,8 @@ inline int make_tensor_map_i32_plain(CUtensorMap* m, const void* base, uint64_t 
   const cuuint32_t box[2] = {box_cols, box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, const_cast<void*>(base), dims, strides, box, estr,
-                         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                         CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(B200MOE_BAD_ARG, "cuTensorMapEncodeTiled (int32) failed with %d", (int)r);
   return B200MOE_OK;
 }

@@ -128,12 +128,13 @@ class MoEGate(nn.Module):
         bias = bias if bias.dtype == torch.float32 else bias.float()
         E = self.n_routed_experts
         scoring = 0 if self.scoring_func == "sigmoid" else 1
-        if x.dtype == torch.bfloat16 and E % 128 == 0 and h % 64 == 0 and T >= 256:
-            # tensor-core path: logits from bf16 MMAs against the weight split into three bf16 parts
+        if x.dtype == torch.bfloat16 and E % 128 == 0 and h % 64 == 0 and T >= 1:
+            # tensor-core path: logits from bf16 MMAs against the weight split into three bf16 parts; the K loop is
+            # split so that a small batch still spreads over many SMs (a decode batch is one m-tile)
             w3 = self._split_weight(w)
-            m_tiles = (T + 127) // 128
+            tiles = ((T + 127) // 128) * ((E + 255) // 256)
             kb = 3 * h // 64
-            ks = max(1, min(8, 148 // m_tiles))
+            ks = max(1, min(16, 148 // tiles))
             while ks > 1 and -(-kb // ks) * (ks - 1) >= kb:
                 ks -= 1
             part = self._scratch(ks * T * E)
@@ -276,7 +277,9 @@ class DeepseekV3MoE(nn.Module):
             self._shared_stream = None
         # int4 methods: up to this many rows per expert group on average the dequantization runs inside the GEMMs
         # (every tile converts its weights once); above it the weights are expanded once per forward instead
-        self.w4_fused_rows_per_group = int(getattr(config, "w4_fused_rows_per_group", 96))
+        # (measured break-even: 64 rows for w4a8, whose tiles hold 64 tokens; 256 for w4a16, whose tiles hold 128)
+        self.w4_fused_rows_per_group = int(getattr(config, "w4_fused_rows_per_group",
+                                                   256 if self.method == "w4a16" else 64))
         self._buffers_cache = {}
         self._status = torch.zeros(1, dtype=torch.int32, device=dev)
         self._last_recv_rows = None
@@ -736,6 +739,33 @@ class DeepseekV3MoE(nn.Module):
             self._buffers_cache[("pairs", name)] = hit
         return hit[1]
 
+    def _raw_nibbles_ok(self, name):
+        """The fused w4a8 GEMM multiplies the raw nibbles and applies (q - z4) * s4 to the dot product, which equals
+        the reference's int8 product (quantization/w4a8_kernel.py:362-380, where the product is cast to int8) only
+        while (q - z4) * s4 stays inside int8 for every nibble the weight holds.  The reference's quantizer keeps it
+        there (:228-262); any weight is checked once here (smallest and largest nibble of every scale group), and one
+        that fails is expanded to int8 instead."""
+        packed, s4, z4 = getattr(self, name + "_qweight"), getattr(self, name + "_s4"), getattr(self, name + "_z4")
+        key = (packed.data_ptr(), packed._version, s4.data_ptr(), s4._version, z4.data_ptr(), z4._version)
+        hit = self._buffers_cache.get(("raw_ok", name))
+        if hit is None or hit[0] != key:
+            W, R8, K = packed.shape                      # nibble i of a word: output row 8 r + i
+            ok = True
+            for e in range(W):                           # one expert at a time keeps the scratch small
+                lo = torch.empty(R8, 8, K // 128, dtype=torch.int32, device=packed.device)
+                hi = torch.empty_like(lo)
+                for i in range(8):
+                    q = ((packed[e] >> (4 * i)) & 15).view(R8, K // 128, 128)
+                    lo[:, i], hi[:, i] = q.amin(-1), q.amax(-1)
+                s, zz = s4[e].to(torch.int32).view(R8, 8, -1), z4[e].to(torch.int32).view(R8, 8, -1)
+                a, b = (lo - zz) * s, (hi - zz) * s
+                ok = ok and bool((torch.minimum(a, b).min() >= -128) & (torch.maximum(a, b).max() <= 127))
+                if not ok:
+                    break
+            hit = (key, ok)
+            self._buffers_cache[("raw_ok", name)] = hit
+        return hit[1]
+
     def _experts_w4a8(self, ctx, buf, rows, seg, widx, down, rng):
         H, I = self.config.hidden_size, self.config.moe_intermediate_size
         a_q, a_s = buf[:, :H].view(torch.int8), buf[:, H:H + (H // 128) * 4].view(torch.float32)
@@ -743,7 +773,7 @@ class DeepseekV3MoE(nn.Module):
         h_q = self._buf("h_i8", (rows, I), torch.int8)
         h_s = self._buf("h_i8_s", (rows, I // 128), torch.float32)
         groups = seg.numel() - 1
-        if (r1 - r0) <= self.w4_fused_rows_per_group * groups:
+        if (r1 - r0) <= self.w4_fused_rows_per_group * groups and self._raw_nibbles_ok("w13") and self._raw_nibbles_ok("w2"):
             # few rows per expert (decode): the packed weights are converted inside the GEMMs, once per tile;
             # act(gate)*up and the int8 re-quantization are GEMM-1's epilogue
             G.grouped_gemm_w4a8(a_q, a_s, self.w13_qweight, self._pairs("w13"), self.w13_weight_scale, seg, widx,

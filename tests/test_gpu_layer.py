@@ -206,6 +206,33 @@ def test_layer_w4a8_decode_shape_reduced():
     assert err < 1e-2, err
 
 
+def test_layer_w4a8_out_of_range_scales_take_the_expanded_path():
+    """The fused w4a8 GEMM is only exact while (q - z4) * s4 fits int8; a weight whose second-level scales break that
+    (none from the reference quantizer does) must be served by the expansion path, whose int8 wrap-around is the
+    reference's (quantization/w4a8_kernel.py:362-380: the product is cast to int8)."""
+    from llm_kernels_b200 import workloads as WL
+    from dataclasses import replace
+    dev = torch.device("cuda:0")
+    shape = replace(WL.CONFIG4, hidden=512, inter=256)
+    x, idx, w = _seeded_router_and_tokens(shape)
+    layer = _build_layer(shape, dev)
+    assert layer._raw_nibbles_ok("w13") and layer._raw_nibbles_ok("w2")
+    y0 = layer.triton_group_gemm_moe_infer(x.to(dev), idx.to(dev), w.to(dev)).clone()
+    layer.w4_fused_rows_per_group = 0                       # force expansion: the two paths agree bit for bit
+    y1 = layer.triton_group_gemm_moe_infer(x.to(dev), idx.to(dev), w.to(dev)).clone()
+    assert torch.equal(y0, y1)
+    layer.w4_fused_rows_per_group = 64
+    layer.w13_s4[0, 0, 0] = 127                             # (q - z) * 127 leaves int8 for q - z >= 2
+    layer.w13_z4[0, 0, 0] = 0
+    layer.w13_qweight[0, 0, 0] |= 0xF                       # make sure such a nibble is present
+    assert not layer._raw_nibbles_ok("w13")
+    y2 = layer.triton_group_gemm_moe_infer(x.to(dev), idx.to(dev), w.to(dev)).clone()
+    layer.w4_fused_rows_per_group = 0
+    y3 = layer.triton_group_gemm_moe_infer(x.to(dev), idx.to(dev), w.to(dev))
+    layer.check_status()
+    assert torch.equal(y2, y3)
+
+
 @pytest.mark.parametrize("n_shared", [1, 2])
 def test_layer_with_shared_experts(n_shared):
     """config.n_shared_experts (reference moe/all2all_moe.py:161-165, 182-183): an unquantized bf16
