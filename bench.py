@@ -350,6 +350,39 @@ def other_configs(dev, peaks, fp8_peak):
     return out
 
 
+def run_w4a8_small(args):
+    """`--shape cfg4-small`: the decode-regime w4a8 layer of configs[4] cut to 64 experts (1.4 GB of packed weights,
+    well above L2, small enough for a profiler capture), 64 tokens top-8 on one GPU.  Prints one JSON line with the
+    device time of the step and of its stages; it is a profiling aid, not the benchmark."""
+    from dataclasses import replace
+    from llm_kernels_b200 import workloads as WL
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    shape = replace(WL.CONFIG4, experts=64)
+    layer = DeepseekV3MoE(WL.make_config(shape), device=dev).eval()
+    WL.fill_layer_gpu(layer, shape)
+    x = WL.tokens(shape, device=dev).view(1, shape.tokens, -1)
+    for _ in range(args.warmup):
+        layer(x)
+    layer.check_status()
+    ms = _time_launches(lambda i: layer(x), args.steps, dev)
+    layer.stage_events = []
+    for _ in range(args.steps):
+        layer(x)
+    torch.cuda.synchronize(dev)
+    ev, st = layer.stage_events, {}
+    for (n0, e0), (n1, e1) in zip(ev[:-1], ev[1:]):
+        if n1 != "start":
+            st[n1] = st.get(n1, 0.0) + e0.elapsed_time(e1) / args.steps
+    wbytes = shape.experts * 3 * shape.hidden * shape.inter // 2
+    print(json.dumps({"metric": "w4a8_decode_layer_ms_per_step", "value": ms, "unit": "ms", "n_gpus": 1,
+                      "steps": args.steps, "warmup": args.warmup, "higher_is_better": False, "dtype": "int4 x int8",
+                      "data": "synthetic", "config": {"workload": "configs[4] with 64 of its 256 experts, 64 tokens top-8"},
+                      "stages_ms": st, "packed_weight_bytes": wbytes,
+                      "packed_weight_gbs_whole_step": wbytes / (ms * 1e-3) / 1e9}), flush=True)
+
+
 def measure_fp8_peak(dev):
     """Dense e4m3 GEMM 8192^3 through torch._scaled_mm (cuBLASLt), TFLOP/s: (burst, sustained).  burst = best of
     12 single launches (the figure for a kernel timed alone); sustained = back-to-back launches for about one
@@ -434,17 +467,20 @@ def run_ours(args):
     # End to end: every step's tokens start in pinned host memory and its output ends in pinned host
     # memory, all inside the timed region.  The loop is the one a serving caller writes: the copy of step
     # i+1's tokens (copy-in stream) and the read-back of step i-1's output (copy-out stream) run on the
-    # copy engines while step i computes; two device input buffers, two host output buffers.
+    # copy engines while step i computes.  Four device input buffers and four host output buffers: the copies may
+    # run a few steps ahead, which absorbs the step-to-step jitter of the host's copy bandwidth when several ranks
+    # share it (every step of the layer waits for the slowest rank's tokens).
     main_stream = torch.cuda.current_stream()
     s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
-    dev_ins = [torch.empty(1, T, H, dtype=torch.bfloat16, device=dev) for _ in range(2)]
-    host_outs = [torch.empty(T, H, dtype=torch.bfloat16).pin_memory() for _ in range(2)]
-    ev_in = [torch.cuda.Event() for _ in range(2)]
-    ev_read = [torch.cuda.Event() for _ in range(2)]       # step finished reading dev_ins[b]
-    ev_done = [torch.cuda.Event() for _ in range(2)]       # host_outs[b] holds its step's output
+    NBUF = 4
+    dev_ins = [torch.empty(1, T, H, dtype=torch.bfloat16, device=dev) for _ in range(NBUF)]
+    host_outs = [torch.empty(T, H, dtype=torch.bfloat16).pin_memory() for _ in range(NBUF)]
+    ev_in = [torch.cuda.Event() for _ in range(NBUF)]
+    ev_read = [torch.cuda.Event() for _ in range(NBUF)]    # step finished reading dev_ins[b]
+    ev_done = [torch.cuda.Event() for _ in range(NBUF)]    # host_outs[b] holds its step's output
 
     def step_e2e(i):
-        b = i & 1
+        b = i % NBUF
         with torch.cuda.stream(s_in):
             s_in.wait_event(ev_read[b])
             dev_ins[b].copy_(host_in[i % nbatch], non_blocking=True)
@@ -487,7 +523,7 @@ def run_ours(args):
     dev_out = torch.empty(T, H, dtype=torch.bfloat16, device=dev)
 
     def copy_only(i):
-        b = i & 1
+        b = i % NBUF
         with torch.cuda.stream(s_in):
             dev_ins[b].copy_(host_in[i % nbatch], non_blocking=True)
         with torch.cuda.stream(s_out):
@@ -615,8 +651,9 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--shape", default="cfg3", choices=["cfg3", "small"],
-                    help="cfg3 = the benchmark configuration; small = 1/8 of its experts and tokens (profiler captures)")
+    ap.add_argument("--shape", default="cfg3", choices=["cfg3", "small", "cfg4-small"],
+                    help="cfg3 = the benchmark configuration; small = 1/8 of its experts and tokens (profiler captures); "
+                         "cfg4-small = only the w4a8 decode layer of configs[4] with 64 experts (profiler captures)")
     ap.add_argument("--ep-passes", type=int, default=1,
                     help="pipeline passes of the EP exchange (N > 1); 1 = exchange and GEMMs back to back")
     ap.add_argument("--ep-exchange", default="auto", choices=["auto", "nccl", "push", "fused"],
@@ -635,6 +672,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.shape == "cfg4-small":
+        run_w4a8_small(args)
     else:
         run_ours(args)
 

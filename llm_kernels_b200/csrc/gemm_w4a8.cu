@@ -39,6 +39,8 @@
 // B200MOE_DEVICE_TIMEOUT to the status word and returns.
 #include <cuda.h>
 
+#include <type_traits>
+
 #include "common.cuh"
 #include "epilogue.cuh"
 #include "ptx.cuh"
@@ -67,19 +69,20 @@ struct Tail8 {
   uint64_t t_full[kTStages], t_empty[kTStages];
   uint64_t x_full[kTStages];                     // the token stage's sums and scales have been written
   uint64_t tmem_full[kAccStages], tmem_empty[kAccStages];
-  uint64_t amax_bar[2];
+  uint64_t stage_full, stage_free;               // fused epilogue: the bf16 stage has been written / read
   uint32_t tmem_base;
   int abort_flag;
   // travelling with a token stage (one K block):
   alignas(16) int32_t rsum[kTStages][kChunk];    // sum of the token's 128 int8 values
   alignas(16) float2 tscale[kTStages][kChunk];   // the token's scale times the block scale of each half
   alignas(16) uint16_t sz[kTStages][256];        // (s4, z4) of the tile's 2 x 128 channels (bulk copies)
-  float amax[2][kPromoWarps][kChunk];
+  alignas(16) __nv_bfloat16 hstage[kChunk][128]; // fused epilogue: act(gate) * up of one tile, [token][channel]
   int32_t seg[kMaxGroups + 1];
   int32_t pref[kMaxGroups + 1];                  // exclusive prefix of token chunks per group
 };
 constexpr size_t kRing8 = size_t(kWStages) * kWBytes + size_t(kTStages) * kTBytes + size_t(kPStages) * kPBytes;
 constexpr size_t kSmem8 = 1024 + kRing8 + sizeof(Tail8);
+static_assert(kSmem8 <= 232448, "shared memory of one CTA");
 
 struct Params8 {
   const float* a_s; int64_t a_s_stride;
@@ -145,7 +148,7 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
       ptx::mbar_init(&sh->t_full[s], 1); ptx::mbar_init(&sh->t_empty[s], 1 + kPromoWarps); ptx::mbar_init(&sh->x_full[s], 1);
     }
     for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&sh->tmem_full[s], 1); ptx::mbar_init(&sh->tmem_empty[s], kPromoWarps); }
-    for (int s = 0; s < 2; ++s) ptx::mbar_init(&sh->amax_bar[s], kPromoWarps);
+    ptx::mbar_init(&sh->stage_full, kPromoWarps); ptx::mbar_init(&sh->stage_free, kPromoWarps);
     sh->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::fence_proxy_async();
@@ -400,6 +403,10 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
       float acc0[kChunk], acc1[kChunk];
 #pragma unroll
       for (int m = 0; m < kChunk; ++m) { acc0[m] = 0.f; acc1[m] = 0.f; }
+      // K loop and epilogue exist once per number of 16-token blocks, so that the code a tile runs is short and straight
+      // (a single version unrolled for 64 tokens spent more time fetching instructions than executing them).
+      auto tile_body = [&](auto nblocks) {
+      constexpr int kBlocks = decltype(nblocks)::value;
       for (int kb = 0; kb < KB; ++kb) {
         // x_full follows t_full (the warp that writes the sums waited for it); waiting for both keeps the bulk copies
         // of the (s4, z4) pairs ordered before this warp's reads
@@ -417,9 +424,9 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
         const int4* rsp = reinterpret_cast<const int4*>(sh->rsum[sr]);
         const float4* tsp = reinterpret_cast<const float4*>(sh->tscale[sr]);
 #pragma unroll
-        for (int mb = 0; mb < kChunk / 16; ++mb) {
-          if (mb * 16 < tl.tn) {
-            const bool more = mb + 1 < kChunk / 16 && (mb + 1) * 16 < tl.tn;
+        for (int mb = 0; mb < kBlocks; ++mb) {
+          {
+            const bool more = mb + 1 < kBlocks;
             tmem_ld_wait16(d0, d1);
             // exact integers: sum_k a_k (q_k - z) s = s (a.q - z sum_k a_k)
 #pragma unroll
@@ -456,59 +463,78 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
         if (++as == kAccStages) { as = 0; pacc ^= 1u; }
         if (++sr == kTStages) { sr = 0; pr ^= 1u; }
       }
-      if (!ok) break;
+      if (!ok) return;
 
       if (!p.fused) {
         const int esize = p.c_dtype == B200MOE_F32 ? 4 : 2;
         uint8_t* dst0 = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(tl.m0) * p.c_stride + static_cast<int64_t>(ch0) * esize;
         uint8_t* dst1 = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(tl.m0) * p.c_stride + static_cast<int64_t>(ch1) * esize;
+        if (p.c_dtype == B200MOE_F32) {
 #pragma unroll
-        for (int m = 0; m < kChunk; ++m) {
-          if (m < tl.rows) {
-            if (p.c_dtype == B200MOE_F32) {
+          for (int m = 0; m < kBlocks * 16; ++m)
+            if (m < tl.rows) {
               *reinterpret_cast<float*>(dst0 + m * p.c_stride) = acc0[m];
               if (second) *reinterpret_cast<float*>(dst1 + m * p.c_stride) = acc1[m];
-            } else if (p.c_dtype == B200MOE_BF16) {
+            }
+        } else if (p.c_dtype == B200MOE_BF16) {
+#pragma unroll
+          for (int m = 0; m < kBlocks * 16; ++m)
+            if (m < tl.rows) {
               *reinterpret_cast<__nv_bfloat16*>(dst0 + m * p.c_stride) = __float2bfloat16_rn(acc0[m]);
               if (second) *reinterpret_cast<__nv_bfloat16*>(dst1 + m * p.c_stride) = __float2bfloat16_rn(acc1[m]);
-            } else {
+            }
+        } else {
+#pragma unroll
+          for (int m = 0; m < kBlocks * 16; ++m)
+            if (m < tl.rows) {
               *reinterpret_cast<__half*>(dst0 + m * p.c_stride) = __float2half_rn(acc0[m]);
               if (second) *reinterpret_cast<__half*>(dst1 + m * p.c_stride) = __float2half_rn(acc1[m]);
             }
-          }
         }
       } else {
         // act(gate) * up with the roundings of the unfused chain (GEMM output, activation and product each rounded
         // to bf16; moe/group_gemm_kernel.py:120-235), then the int8 1x128 quantizer of
         // quantization/w4a8_kernel.py:145-168: s = amax / 127, y = floor(h / s + 0.5), s stored after an f16 rounding.
-        // A token's 128 channels sit in the 128 threads of the four warps: warp maximum, then shared memory.
-        const int buf = epi_n & 1;
+        // The products go through a [token][channel] bf16 stage in shared memory (exact: they are bf16 values), so
+        // that a warp then owns whole tokens: maximum by shuffles, four channels per lane, one 128-byte row per store.
+        const uint32_t par = static_cast<uint32_t>(epi_n & 1);
+        if (!warp_wait(&sh->stage_free, par ^ 1u, abort_flag)) { ok = false; return; }     // previous tile's readers are done
 #pragma unroll
-        for (int m = 0; m < kChunk; ++m) {
-          if (m < tl.tn) {
-            const float g = bf16r(acc0[m]);
-            const float u = bf16r(acc1[m]);
-            const float h = bf16r(bf16r(gate_act(g, p.act)) * u);
-            acc0[m] = h;
-            const uint32_t mx = __reduce_max_sync(0xffffffffu, __float_as_uint(fabsf(h)));   // order of non-negative floats
-            if (lane == 0) sh->amax[buf][q][m] = __uint_as_float(mx);
-          }
+        for (int m = 0; m < kBlocks * 16; ++m) {
+          const float g = bf16r(acc0[m]);
+          const float u = bf16r(acc1[m]);
+          sh->hstage[m][c] = __float2bfloat16_rn(bf16r(gate_act(g, p.act)) * u);
         }
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(&sh->amax_bar[buf]);
-        if (!warp_wait(&sh->amax_bar[buf], (epi_n >> 1) & 1u, abort_flag)) { ok = false; break; }
+        if (lane == 0) ptx::mbar_arrive(&sh->stage_full);
+        if (!warp_wait(&sh->stage_full, par, abort_flag)) { ok = false; return; }
         ++epi_n;
-        uint8_t* dst = static_cast<uint8_t*>(p.c) + static_cast<int64_t>(tl.m0) * p.c_stride + tl.ct * 128 + c;
+        for (int m = q; m < tl.rows; m += kPromoWarps) {
+          const uint2 hv = *reinterpret_cast<const uint2*>(&sh->hstage[m][lane * 4]);
+          const float h[4] = {__uint_as_float(hv.x << 16), __uint_as_float(hv.x & 0xFFFF0000u),
+                              __uint_as_float(hv.y << 16), __uint_as_float(hv.y & 0xFFFF0000u)};
+          float amax = fmaxf(fmaxf(fabsf(h[0]), fabsf(h[1])), fmaxf(fabsf(h[2]), fabsf(h[3])));
 #pragma unroll
-        for (int m = 0; m < kChunk; ++m) {
-          if (m < tl.rows) {
-            const float amax = fmaxf(fmaxf(sh->amax[buf][0][m], sh->amax[buf][1][m]), fmaxf(sh->amax[buf][2][m], sh->amax[buf][3][m]));
-            const float scale = __fdiv_rn(amax, 127.f);
-            const float rq = floorf(__fdiv_rn(acc0[m], scale) + 0.5f);
-            dst[m * p.c_stride] = static_cast<uint8_t>(__float2int_rz(fminf(fmaxf(rq, -128.f), 127.f)) & 0xFF);
-            if (c == 0) p.c_s[static_cast<int64_t>(tl.m0 + m) * p.c_s_stride + tl.ct] = __half2float(__float2half_rn(scale));
+          for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+          const float scale = __fdiv_rn(amax, 127.f);
+          uint32_t packed = 0;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float rq = floorf(__fdiv_rn(h[i], scale) + 0.5f);
+            packed |= (static_cast<uint32_t>(__float2int_rz(fminf(fmaxf(rq, -128.f), 127.f))) & 0xFFu) << (8 * i);
           }
+          *reinterpret_cast<uint32_t*>(static_cast<uint8_t*>(p.c) + static_cast<int64_t>(tl.m0 + m) * p.c_stride + tl.ct * 128 + lane * 4) = packed;
+          if (lane == 0) p.c_s[static_cast<int64_t>(tl.m0 + m) * p.c_s_stride + tl.ct] = __half2float(__float2half_rn(scale));
         }
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive(&sh->stage_free);
+      }
+      };
+      switch (tl.tn >> 4) {
+        case 1: tile_body(std::integral_constant<int, 1>{}); break;
+        case 2: tile_body(std::integral_constant<int, 2>{}); break;
+        case 3: tile_body(std::integral_constant<int, 3>{}); break;
+        default: tile_body(std::integral_constant<int, 4>{}); break;
       }
     }
   }
