@@ -150,12 +150,15 @@ B200MOE_API int b200moe_router_topk(const void* x, int x_dtype, const float* w, 
  * MMAs: w3 bf16 [E, 3H] holds, per expert row, the three bf16 parts hi | mid | lo of the f32
  * router weight (hi = bf16(w), mid = bf16(w - hi), lo = bf16(w - hi - mid)); x is bf16
  * [T,H].  The K loop is split over `ksplits` CTAs per tile; partials f32 [ksplits, T, E]
- * receives the partial sums.  E % 128 == 0, H % 64 == 0.
+ * receives the partial sums.  E % 128 == 0, H % 64 == 0; a model with another expert count
+ * pads w3 with zero rows to the next multiple of 128 and passes the padded count here.
  * b200moe_router_select: adds the partials in index order and applies the scoring,
- * group-limited selection and weight normalisation exactly as b200moe_router_topk. */
+ * group-limited selection and weight normalisation exactly as b200moe_router_topk, over
+ * the first E columns of rows that are partials_row_stride floats apart (the padded count). */
 B200MOE_API int b200moe_router_logits_bf16x3(const void* x_bf16, const void* w3_bf16, float* partials,
                                  int64_t T, int64_t H, int E, int ksplits, void* stream);
-B200MOE_API int b200moe_router_select(const float* partials, int nsplit, const float* bias, int64_t T, int E,
+B200MOE_API int b200moe_router_select(const float* partials, int nsplit, int64_t partials_row_stride,
+                          const float* bias, int64_t T, int E,
                           int top_k, int n_group, int topk_group, int scoring,
                           int norm_topk_prob, float routed_scaling_factor, int64_t* topk_idx,
                           float* topk_weight, void* stream);

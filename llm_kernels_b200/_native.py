@@ -37,7 +37,7 @@ SIGNATURES = {
     "b200moe_dequant_sum": (_i, [_p, _i, _i64, _i64, _p, _i, _i64, _i64, _i, _i64, _i64, _p, _i, _p]),
     "b200moe_router_topk": (_i, [_p, _i, _p, _p, _i64, _i64, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p]),
     "b200moe_router_logits_bf16x3": (_i, [_p, _p, _p, _i64, _i64, _i, _i, _p]),
-    "b200moe_router_select": (_i, [_p, _i, _p, _i64, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p]),
+    "b200moe_router_select": (_i, [_p, _i, _i64, _p, _i64, _i, _i, _i, _i, _i, _i, _f, _p, _p, _p]),
     "b200moe_route_metadata_workspace_bytes": (_sz, [_i64, _i]),
     "b200moe_route_metadata": (_i, [_p, _i64, _i, _p, _p, _p, _p, _sz, _p]),
     "b200moe_route_metadata_noalloc": (_i, [_p, _i64, _i, _p, _p, _p, _p]),

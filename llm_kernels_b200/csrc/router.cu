@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(256) router_tiled_kernel(const T* __restrict__
 
 // ---- selection from precomputed logits (tensor-core path) ----------------------------------
 __global__ void __launch_bounds__(256) router_select_kernel(const float* __restrict__ partials,
-                                                            int nsplit, RouterParams p) {
+                                                            int nsplit, int64_t row_stride, RouterParams p) {
   extern __shared__ __align__(16) float smem[];   // [8 warps][2][E]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int64_t t = static_cast<int64_t>(blockIdx.x) * 8 + warp;
@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(256) router_select_kernel(const float* __restr
   float* sf = lg + p.E;
   for (int e = lane; e < p.E; e += 32) {
     float v = 0.f;
-    for (int s = 0; s < nsplit; ++s) v += partials[(static_cast<int64_t>(s) * p.T + t) * p.E + e];
+    for (int s = 0; s < nsplit; ++s) v += partials[(static_cast<int64_t>(s) * p.T + t) * row_stride + e];
     lg[e] = v;
   }
   __syncwarp();
@@ -286,12 +286,14 @@ extern "C" int b200moe_router_topk(const void* x, int x_dtype, const float* w, c
   }
 }
 
-extern "C" int b200moe_router_select(const float* partials, int nsplit, const float* bias, int64_t T, int E,
+extern "C" int b200moe_router_select(const float* partials, int nsplit, int64_t partials_row_stride,
+                                     const float* bias, int64_t T, int E,
                                      int top_k, int n_group, int topk_group, int scoring,
                                      int norm_topk_prob, float routed_scaling_factor, int64_t* topk_idx,
                                      float* topk_weight, void* stream) {
   B200MOE_REQUIRE(partials && topk_idx && topk_weight, B200MOE_BAD_ARG, "router_select: null pointer");
-  B200MOE_REQUIRE(nsplit >= 1 && T >= 0 && E >= 1 && E <= 1024, B200MOE_BAD_SHAPE, "router_select: nsplit=%d E=%d", nsplit, E);
+  B200MOE_REQUIRE(nsplit >= 1 && T >= 0 && E >= 1 && E <= 1024 && partials_row_stride >= E, B200MOE_BAD_SHAPE,
+                  "router_select: nsplit=%d E=%d row stride %lld", nsplit, E, (long long)partials_row_stride);
   B200MOE_REQUIRE(top_k >= 1 && top_k <= kMaxTopK && top_k <= E, B200MOE_BAD_SHAPE, "router_select: top_k=%d", top_k);
   B200MOE_REQUIRE(n_group >= 1 && n_group <= 32 && E % n_group == 0 && topk_group >= 1 && topk_group <= n_group &&
                   (n_group == 1 || E / n_group >= 2), B200MOE_BAD_SHAPE, "router_select: n_group=%d topk_group=%d", n_group, topk_group);
@@ -304,6 +306,6 @@ extern "C" int b200moe_router_select(const float* partials, int nsplit, const fl
   const size_t smem = sizeof(float) * 8 * 2 * E;
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  router_select_kernel<<<grid, 256, smem, as_stream(stream)>>>(partials, nsplit, p);
+  router_select_kernel<<<grid, 256, smem, as_stream(stream)>>>(partials, nsplit, partials_row_stride, p);
   return check_launch("router_select");
 }

@@ -128,19 +128,25 @@ class MoEGate(nn.Module):
         bias = bias if bias.dtype == torch.float32 else bias.float()
         E = self.n_routed_experts
         scoring = 0 if self.scoring_func == "sigmoid" else 1
-        if x.dtype == torch.bfloat16 and E % 128 == 0 and h % 64 == 0 and T >= 1:
-            # tensor-core path: logits from bf16 MMAs against the weight split into three bf16 parts; the K loop is
-            # split so that a small batch still spreads over many SMs (a decode batch is one m-tile)
+        if x.dtype == torch.bfloat16 and h % 64 == 0 and T >= 1:
+            # tensor-core path: logits from bf16 MMAs against the weight split into three bf16 parts (zero rows pad
+            # the expert count to a multiple of 128); the K loop is split so that a small batch still spreads over
+            # many SMs (a decode batch is one m-tile)
             w3 = self._split_weight(w)
-            tiles = ((T + 127) // 128) * ((E + 255) // 256)
+            Ep = w3.shape[0]
+            tiles = ((T + 127) // 128) * ((Ep + 255) // 256)
             kb = 3 * h // 64
-            ks = max(1, min(16, 148 // tiles))
+            # Splits also bound the length of one tensor-core accumulation (about 16 K blocks of 64): the f32
+            # accumulator of the MMA truncates, and the error of a long chain reaches the routing weights (measured
+            # 5e-5 relative for 4096-term dot products in two splits, below 1e-5 with short chains); the partial sums
+            # are added with IEEE roundings by the selection kernel.
+            ks = max(1, min(16, max(148 // tiles, -(-kb // 16))))
             while ks > 1 and -(-kb // ks) * (ks - 1) >= kb:
                 ks -= 1
-            part = self._scratch(ks * T * E)
-            N.check(N.lib().b200moe_router_logits_bf16x3(N.ptr(x), N.ptr(w3), N.ptr(part), T, h, E, ks, N.stream()))
+            part = self._scratch(ks * T * Ep)
+            N.check(N.lib().b200moe_router_logits_bf16x3(N.ptr(x), N.ptr(w3), N.ptr(part), T, h, Ep, ks, N.stream()))
             N.check(N.lib().b200moe_router_select(
-                N.ptr(part), ks, N.ptr(bias), T, E, self.top_k, self.n_group, self.topk_group, scoring,
+                N.ptr(part), ks, Ep, N.ptr(bias), T, E, self.top_k, self.n_group, self.topk_group, scoring,
                 1 if self.norm_topk_prob else 0, float(self.routed_scaling_factor),
                 N.ptr(topk_idx), N.ptr(topk_weight), N.stream()))
         else:
@@ -152,14 +158,19 @@ class MoEGate(nn.Module):
         return topk_idx, topk_weight
 
     def _split_weight(self, w):
-        """[hi | mid | lo] bf16 parts of the f32 router weight, [E, 3H]; rebuilt when the weight changes."""
+        """[hi | mid | lo] bf16 parts of the f32 router weight, [E rounded up to a multiple of 128, 3H] (zero rows
+        after the last expert); rebuilt when the weight changes."""
         key = (w.data_ptr(), w._version, tuple(w.shape))
         if getattr(self, "_w3_key", None) != key:
             hi = w.to(torch.bfloat16)
             r1 = w - hi.float()
             mid = r1.to(torch.bfloat16)
             lo = (r1 - mid.float()).to(torch.bfloat16)
-            self._w3 = torch.cat([hi, mid, lo], dim=1).contiguous()
+            w3 = torch.cat([hi, mid, lo], dim=1)
+            pad = -w.shape[0] % 128
+            if pad:
+                w3 = torch.cat([w3, w3.new_zeros(pad, w3.shape[1])], dim=0)
+            self._w3 = w3.contiguous()
             self._w3_key = key
         return self._w3
 

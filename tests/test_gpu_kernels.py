@@ -147,11 +147,14 @@ def _check_router(dev, x, W, bias, k, ng, tg, scoring, scale, ref=None):
     gi, gw = R.canonical_rows(idx.cpu(), w.cpu())
     ci, cw = R.canonical_rows(oi, ow)
     assert torch.equal(gi[ok], ci[ok]), "top-k index sets must be bit-exact"
-    torch.testing.assert_close(gw[ok], cw[ok], rtol=2e-6, atol=1e-7)
+    # weights: the logits are f32 sums of up to 7168 exact products taken in another order than the oracle's (here
+    # in up to 16 partial sums of tensor-core accumulations); the difference reaches the normalised weight as a few
+    # 1e-6 relative (measured: at most 6.2e-6 over the benchmark configurations)
+    torch.testing.assert_close(gw[ok], cw[ok], rtol=1e-5, atol=1e-6)
     if ref is not None:
         ri, rw = R.canonical_rows(*ref)
         assert torch.equal(gi[ok], ri[ok])
-        torch.testing.assert_close(gw[ok], rw[ok], rtol=2e-6, atol=1e-7)
+        torch.testing.assert_close(gw[ok], rw[ok], rtol=1e-5, atol=1e-6)
 
 
 @pytest.mark.parametrize("case", ["gate_small", "gate_v3", "gate_flat"])
