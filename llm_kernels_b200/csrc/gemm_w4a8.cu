@@ -248,7 +248,9 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
         // D s32, A and B signed int8; bit 15: the A operand (weights) is channel-major in shared memory
         const uint32_t idesc = ptx::umma_idesc(2, 1, 1, 128, static_cast<uint32_t>(tl.tn)) | (1u << 15);
         for (int kb = 0; kb < KB; ++kb) {
-          if (!ptx::mbar_wait(&sh->w_full[sw], pw, abort_flag) || !ptx::mbar_wait(&sh->t_full[st], pt, abort_flag) ||
+          // x_full (sums written) follows t_full (tokens and pairs landed): the warp that arrives on it waited for
+          // t_full.  Waiting for it here lets the promotion warps wait for tmem_full alone.
+          if (!ptx::mbar_wait(&sh->w_full[sw], pw, abort_flag) || !ptx::mbar_wait(&sh->x_full[st], pt, abort_flag) ||
               !ptx::mbar_wait(&sh->tmem_empty[as], pacc ^ 1u, abort_flag)) { ok = false; break; }
           ptx::tc_fence_after_sync();
           const uint32_t d = tmem_base + static_cast<uint32_t>(as) * 128u;
@@ -408,11 +410,9 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
       auto tile_body = [&](auto nblocks) {
       constexpr int kBlocks = decltype(nblocks)::value;
       for (int kb = 0; kb < KB; ++kb) {
-        // x_full follows t_full (the warp that writes the sums waited for it); waiting for both keeps the bulk copies
-        // of the (s4, z4) pairs ordered before this warp's reads
-        if (!warp_wait(&sh->tmem_full[as], pacc, abort_flag) ||
-            !warp_wait(&sh->x_full[sr], pr, abort_flag) ||
-            !warp_wait(&sh->t_full[sr], pr, abort_flag)) { ok = false; break; }
+        // tmem_full alone: the MMAs of this K block were issued after x_full, which follows t_full, so the sums, the
+        // scales and the (s4, z4) pairs of this stage are in place (acquire/release chain over the three barriers)
+        if (!warp_wait(&sh->tmem_full[as], pacc, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after_sync();
         const uint32_t tcol = tmem_base + lane_base + static_cast<uint32_t>(as) * 128u;
         uint32_t d0[16], d1[16];                       // one 16-token block of each half; the next block's load is
@@ -427,12 +427,16 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
         for (int mb = 0; mb < kBlocks; ++mb) {
           {
             const bool more = mb + 1 < kBlocks;
+            int4 rq[4];
+            float4 tq[8];
+#pragma unroll
+            for (int j4 = 0; j4 < 4; ++j4) { rq[j4] = rsp[mb * 4 + j4]; tq[2 * j4] = tsp[mb * 8 + j4 * 2]; tq[2 * j4 + 1] = tsp[mb * 8 + j4 * 2 + 1]; }
             tmem_ld_wait16(d0, d1);
             // exact integers: sum_k a_k (q_k - z) s = s (a.q - z sum_k a_k)
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
-              const int4 r4 = rsp[mb * 4 + j4];
-              const float4 ta = tsp[mb * 8 + j4 * 2], tb = tsp[mb * 8 + j4 * 2 + 1];
+              const int4 r4 = rq[j4];
+              const float4 ta = tq[2 * j4], tb = tq[2 * j4 + 1];
               const int rs[4] = {r4.x, r4.y, r4.z, r4.w};
               const float ts0[4] = {ta.x, ta.z, tb.x, tb.z};
 #pragma unroll
@@ -444,8 +448,8 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
             if (more) ptx::tmem_ld16(tcol + (mb + 1) * 16, d0);
 #pragma unroll
             for (int j4 = 0; j4 < 4; ++j4) {
-              const int4 r4 = rsp[mb * 4 + j4];
-              const float4 ta = tsp[mb * 8 + j4 * 2], tb = tsp[mb * 8 + j4 * 2 + 1];
+              const int4 r4 = rq[j4];
+              const float4 ta = tq[2 * j4], tb = tq[2 * j4 + 1];
               const int rs[4] = {r4.x, r4.y, r4.z, r4.w};
               const float ts1[4] = {ta.y, ta.w, tb.y, tb.w};
 #pragma unroll
