@@ -394,7 +394,7 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
     const int c = (tl_lane & ~7) + ((tl_lane & 3) << 1) + ((tl_lane >> 2) & 1);
     const uint32_t lane_base = static_cast<uint32_t>(q * 32) << 16;
     int as = 0, sr = 0, epi_n = 0;
-    uint32_t pacc = 0, pr = 0;
+    uint32_t pacc = 0;
     bool ok = true;
     for (int t = first; ok && t < total_tiles; t += step) {
       const Tile8 tl = decode_tile8(sh, p, t, num_ct);
@@ -465,7 +465,7 @@ gemm_w4a8_kernel(const __grid_constant__ RowMaps tmap_a, const __grid_constant__
         __syncwarp();
         if (lane == 0) { ptx::mbar_arrive(&sh->tmem_empty[as]); ptx::mbar_arrive(&sh->t_empty[sr]); }
         if (++as == kAccStages) { as = 0; pacc ^= 1u; }
-        if (++sr == kTStages) { sr = 0; pr ^= 1u; }
+        if (++sr == kTStages) sr = 0;
       }
       if (!ok) return;
 
