@@ -275,3 +275,24 @@ def test_quantized_allreduce_plumbing_gloo(tmp_path, world):
     for p in procs:
         out, _ = p.communicate(timeout=180)
         assert p.returncode == 0, out
+
+
+def test_raw_nibble_range_check_of_the_fused_w4a8_path():
+    """DeepseekV3MoE._raw_nibbles_ok decides whether the fused w4a8 GEMM (raw nibbles on the tensor core, (q - z4) * s4
+    applied to the dot product) may serve a weight: it must accept the reference quantizer's output
+    (quantization/w4a8_kernel.py:228-262) and reject a weight whose (q - z4) * s4 leaves int8 for a nibble it holds
+    (the reference casts that product to int8, :362-380).  Pure tensor arithmetic: runs on the host."""
+    from types import SimpleNamespace
+    from oracle import restate as R
+    from llm_kernels_b200.moe.all2all_moe import DeepseekV3MoE
+    g = torch.Generator().manual_seed(5)
+    packed, _, s4, z4 = R.w4a8_weight_quant(torch.randn(256, 512, generator=g) * 0.05)[:4]
+    fake = SimpleNamespace(w13_qweight=packed[None].clone(), w13_s4=s4[None].clone(), w13_z4=z4[None].clone(),
+                           _buffers_cache={})
+    assert DeepseekV3MoE._raw_nibbles_ok(fake, "w13")
+    fake.w13_s4[0, 0, 0] = 127
+    fake.w13_z4[0, 0, 0] = 0
+    fake.w13_qweight[0, 0, 0] |= 0xF                       # a nibble 15 in that scale group: 15 * 127 wraps in int8
+    assert not DeepseekV3MoE._raw_nibbles_ok(fake, "w13")
+    fake.w13_qweight[0, 0, :128] &= ~0xF                   # no nibble above 0 left in the group: (0 - 0) * 127 fits
+    assert DeepseekV3MoE._raw_nibbles_ok(fake, "w13")
