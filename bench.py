@@ -617,6 +617,20 @@ def run_ours(args):
                              "frac_of_nominal_fp8_4500": (g1_flops + g2_flops) / (g1_s + g2_s) / 1e12 / NOMINAL_FP8_TFLOPS,
                              "fp8_peak_measured_tflops": fp8_peak, "fp8_peak_sustained_tflops": fp8_sustained},
         }
+        if world > 1:
+            # Expert-parallel exchange on rank 0: rows that arrive from / return to the other ranks (about
+            # (N-1)/N of the rows it computes), bytes of their records and results, and what of the exchange is not
+            # hidden: the plan, the permute + push + barrier stage beyond the time the same kernel needs for its HBM
+            # traffic alone, and the down projection's remote stores (GEMM in the step minus the GEMM alone).
+            rec = H + (H // 128) * 4
+            remote_rows = rows * (world - 1) / world
+            local_permute_ms = (T * H * 2 + T * k * rec) / (peaks["hbm_gbs"] * 1e9) * 1e3
+            push_ms = max(stages.get("permute_quant", 0.0) - local_permute_ms, 1e-6)
+            ret_ms = max(stages.get("gemm2", 0.0) - g2_ms, 0.0)
+            line["nvlink"] = {
+                "dispatch_bytes": remote_rows * rec, "dispatch_gbs": remote_rows * rec / (push_ms * 1e-3) / 1e9,
+                "return_bytes": remote_rows * H * 2, "return_extra_ms": ret_ms,
+                "exposed_ms": stages.get("exchange_plan", 0.0) + push_ms + ret_ms}
         if parity is not None:
             line["parity"] = parity
         if world == 1 and args.cpu_tokens > 0:

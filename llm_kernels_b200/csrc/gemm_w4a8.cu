@@ -10,9 +10,9 @@
 //   * The dot product of a token row a with w8 = (q - z) * s over one 128-wide K block (one (s, z) per output channel
 //     and K block) is  s * (a . q  -  z * sum_k a_k).  So the tensor core multiplies the int8 tokens with the RAW
 //     nibbles q (0..15 as int8) and the promotion restores the exact integer with two integer multiply-adds per value.
-//     This equals the reference's int8 product whenever (q - z) * s fits int8 for q = 0 and q = 15, which its
-//     quantizer guarantees (quantization/w4a8_kernel.py:228-262); the Python wrapper checks it once per weight and
-//     otherwise expands the weight to int8.
+//     This equals the reference's int8 product whenever (q - z) * s fits int8 for every nibble q the weight holds,
+//     which its quantizer guarantees (quantization/w4a8_kernel.py:228-262); the Python layer checks it once per
+//     weight (smallest and largest nibble of every scale group) and otherwise expands the weight to int8.
 //   * Output channels are the M = 128 rows of the MMA and the tokens its N = 16..64 columns: a thread of the promotion
 //     warps owns one channel, keeps that channel's (s, z) in registers and touches only as many accumulators as there
 //     are tokens, so the per-K-block work of the CUDA cores shrinks with the batch instead of staying at 128 x 256.
